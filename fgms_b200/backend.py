@@ -1,0 +1,212 @@
+"""PyTorch binding with the operator surface of ``FGMS.backend``.
+
+The reference exports three functions from ``backend/pybind_cuda.cpp:8-10`` (prototypes in
+``backend/spconv.h:10-49``).  The functions below keep their names, positional signatures,
+in-place accumulate semantics and error behaviour, and forward to the C ABI of
+``libfgms_b200.so`` with raw device pointers — this file is the only torch-aware layer.
+
+Differences from the reference, all deliberate:
+
+* kernels run on PyTorch's *current* stream, not on the legacy default stream
+  (``backend/spconv.cu:73``);
+* arguments are validated (device, dtype, contiguity, shapes) and raise ``ValueError`` instead
+  of reading out of bounds;
+* fp16 accumulates in fp32 (the reference accumulates in fp16, ``backend/fwd_kernels.cuh:66``);
+* ``arch80`` selects the arithmetic for fp32 storage in the backward as well as the forward
+  (``True`` → tf32 tensor cores, ``False`` → exact fp32 FFMA); the reference's backward ignores
+  the flag and always uses tf32 (``backend/spconv.cu:551-570``).
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+__all__ = ["fgms_fusion_fwd_cuda", "fgms_fwd_cuda", "fgms_bwd_cuda", "fgms_dgrad_cuda", "fgms_wgrad_cuda",
+           "wgrad_workspace", "kernel_family", "device_status", "launch_count"]
+
+_L = _lib.lib
+
+
+def _dtype_math(t: torch.Tensor, arch80: bool):
+    if t.dtype == torch.float16:
+        return _lib.DTYPE_F16, _lib.MATH_F16
+    if t.dtype == torch.float32:
+        return _lib.DTYPE_F32, (_lib.MATH_TF32 if arch80 else _lib.MATH_FP32)
+    raise ValueError(f"unsupported feature dtype {t.dtype}: the operator takes float16 or float32")
+
+
+def _check_feat(name, t, dtype=None, dim=2):
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise ValueError(f"{name} must be a CUDA tensor")
+    if t.dim() != dim:
+        raise ValueError(f"{name} must have {dim} dimensions, got {t.dim()}")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise ValueError(f"{name} must have dtype {dtype}, got {t.dtype}")
+
+
+def _check_index(name, t, device, min_len=None, cuda=True):
+    if not isinstance(t, torch.Tensor) or t.dtype != torch.int32:
+        raise ValueError(f"{name} must be an int32 tensor")
+    if cuda and (not t.is_cuda or t.device != device):
+        raise ValueError(f"{name} must live on {device}")
+    if not cuda and t.is_cuda:
+        raise ValueError(f"{name} must be a CPU tensor")
+    if not t.is_contiguous():
+        raise ValueError(f"{name} must be contiguous")
+    if min_len is not None and t.numel() < min_len:
+        raise ValueError(f"{name} needs at least {min_len} entries, got {t.numel()}")
+
+
+def _ptr(t):
+    return t.data_ptr() if t is not None and t.numel() > 0 else None
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _common(in_feats, kernel, kpos, in_map, out_map):
+    _check_feat("in_feats", in_feats)
+    _check_feat("kernel", kernel, in_feats.dtype, dim=3)
+    k_vol = kernel.size(0)
+    _check_index("kpos", kpos, in_feats.device, k_vol + 1)
+    _check_index("in_map", in_map, in_feats.device)
+    _check_index("out_map", out_map, in_feats.device)
+    if in_map.numel() != out_map.numel():
+        raise ValueError("in_map and out_map differ in length")
+    return k_vol
+
+
+_ws_cache: dict = {}
+
+
+def wgrad_workspace(c_in: int, c_out: int, k_vol: int, device) -> torch.Tensor:
+    """fp32 scratch buffer the fp16 weight-gradient needs (cached per device and size)."""
+    nbytes = _L.fgms_b200_wgrad_workspace_bytes(c_in, c_out, k_vol, _lib.DTYPE_F16)
+    key = (torch.device(device), nbytes)
+    ws = _ws_cache.get(key)
+    if ws is None:
+        ws = torch.empty(max(nbytes // 4, 64), dtype=torch.float32, device=device)
+        _ws_cache[key] = ws
+    return ws
+
+
+def fgms_fusion_fwd_cuda(in_feats, kernel, sum_nnz, out_feats, kpos, qkpos, in_map, out_map,
+                         separate_mid, arch80):
+    """Fused forward — ``ConvolutionForwardFused`` (``backend/spconv.cu:23-246``).
+
+    ``out_feats[out_map[j]] += in_feats[in_map[j]] @ kernel[k(j)]`` for every pair; with
+    ``separate_mid`` the centre offset is applied densely and ``out_feats`` is overwritten."""
+    k_vol = _common(in_feats, kernel, kpos, in_map, out_map)
+    _check_feat("out_feats", out_feats, in_feats.dtype)
+    if qkpos is not None:
+        _check_index("qkpos", qkpos, in_feats.device, k_vol + 1)
+    if out_feats.size(1) != kernel.size(2):
+        raise ValueError("out_feats width differs from the kernel's output channels")
+    dtype, math = _dtype_math(in_feats, arch80)
+    with torch.cuda.device(in_feats.device):
+        _lib.check(_L.fgms_b200_fusion_fwd(
+            _ptr(in_feats), _ptr(kernel), _ptr(out_feats), _ptr(kpos), _ptr(qkpos), _ptr(in_map), _ptr(out_map),
+            in_feats.size(0), out_feats.size(0), in_feats.size(1), kernel.size(1), kernel.size(2), k_vol,
+            int(sum_nnz), dtype, math, int(bool(separate_mid)), _stream()))
+
+
+def fgms_fwd_cuda(in_feats, kernel, sum_nnz, out_feats, kernel_nnz, kernel_pos, in_map, out_map,
+                  separate_mid, arch80):
+    """Per-offset forward — ``ConvolutionForward`` (``backend/spconv.cu:249-411``).
+    ``kernel_nnz`` is a CPU int32 tensor as in the reference (``spconv.cu:308``)."""
+    k_vol = _common(in_feats, kernel, kernel_pos, in_map, out_map)
+    _check_feat("out_feats", out_feats, in_feats.dtype)
+    _check_index("kernel_nnz", kernel_nnz, None, k_vol, cuda=False)
+    if out_feats.size(1) != kernel.size(2):
+        raise ValueError("out_feats width differs from the kernel's output channels")
+    dtype, math = _dtype_math(in_feats, arch80)
+    with torch.cuda.device(in_feats.device):
+        _lib.check(_L.fgms_b200_seq_fwd(
+            _ptr(in_feats), _ptr(kernel), _ptr(out_feats), kernel_nnz.data_ptr(), _ptr(kernel_pos), _ptr(in_map),
+            _ptr(out_map), in_feats.size(0), out_feats.size(0), in_feats.size(1), kernel.size(1), kernel.size(2),
+            k_vol, int(sum_nnz), dtype, math, int(bool(separate_mid)), _stream()))
+
+
+def fgms_bwd_cuda(out_feats_grad, in_feats, kernel, sum_nnz, in_feats_grad, kernel_grad, kpos, qkpos,
+                  in_map, out_map, separate_mid, arch80):
+    """Backward — ``ConvolutionBackward`` (``backend/spconv.cu:414-571``): accumulates the input
+    gradient into ``in_feats_grad`` and the weight gradient into ``kernel_grad``."""
+    k_vol = _common(in_feats, kernel, kpos, in_map, out_map)
+    _check_feat("out_feats_grad", out_feats_grad, in_feats.dtype)
+    _check_feat("in_feats_grad", in_feats_grad, in_feats.dtype)
+    _check_feat("kernel_grad", kernel_grad, in_feats.dtype, dim=3)
+    if in_feats.size(1) == kernel.size(1):
+        if in_feats_grad.shape != in_feats.shape or kernel_grad.shape != kernel.shape:
+            raise ValueError("gradient buffers must have the shapes of in_feats and kernel")
+        if out_feats_grad.size(1) != kernel.size(2):
+            raise ValueError("out_feats_grad width differs from the kernel's output channels")
+    dtype, math = _dtype_math(in_feats, arch80)
+    ws = wgrad_workspace(kernel.size(1), kernel.size(2), k_vol, in_feats.device) if dtype == _lib.DTYPE_F16 else None
+    with torch.cuda.device(in_feats.device):
+        _lib.check(_L.fgms_b200_bwd(
+            _ptr(out_feats_grad), _ptr(in_feats), _ptr(kernel), _ptr(in_feats_grad), _ptr(kernel_grad), _ptr(kpos),
+            _ptr(qkpos), _ptr(in_map), _ptr(out_map), in_feats.size(0), out_feats_grad.size(0), in_feats.size(1),
+            kernel.size(1), kernel.size(2), k_vol, int(sum_nnz), dtype, math, int(bool(separate_mid)),
+            _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream()))
+
+
+def fgms_dgrad_cuda(out_feats_grad, kernel, in_feats_grad, kpos, in_map, out_map, arch80):
+    """Input gradient alone (first half of ``ConvolutionBackward``, ``backend/spconv.cu:454-461``)."""
+    k_vol = _common(in_feats_grad, kernel, kpos, in_map, out_map)
+    _check_feat("out_feats_grad", out_feats_grad, kernel.dtype)
+    dtype, math = _dtype_math(kernel, arch80)
+    with torch.cuda.device(kernel.device):
+        _lib.check(_L.fgms_b200_dgrad(
+            _ptr(out_feats_grad), _ptr(kernel), _ptr(in_feats_grad), _ptr(kpos), _ptr(in_map), _ptr(out_map),
+            in_feats_grad.size(0), out_feats_grad.size(0), kernel.size(1), kernel.size(2), k_vol, dtype, math,
+            _stream()))
+
+
+def fgms_wgrad_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map, out_map, arch80,
+                    workspace=None, accumulate=True):
+    """Weight gradient alone (second half of ``ConvolutionBackward``, ``backend/spconv.cu:495-569``).
+    For fp16 the fp32 partial sums of this call are left in ``workspace`` (returned)."""
+    k_vol = kernel_grad.size(0)
+    _check_feat("in_feats", in_feats)
+    _check_feat("out_feats_grad", out_feats_grad, in_feats.dtype)
+    _check_feat("kernel_grad", kernel_grad, in_feats.dtype, dim=3)
+    _check_index("kpos", kpos, in_feats.device, k_vol + 1)
+    _check_index("in_map", in_map, in_feats.device)
+    _check_index("out_map", out_map, in_feats.device)
+    dtype, math = _dtype_math(in_feats, arch80)
+    if dtype == _lib.DTYPE_F16 and workspace is None:
+        workspace = wgrad_workspace(kernel_grad.size(1), kernel_grad.size(2), k_vol, in_feats.device)
+    with torch.cuda.device(in_feats.device):
+        _lib.check(_L.fgms_b200_wgrad(
+            _ptr(in_feats), _ptr(out_feats_grad), _ptr(kernel_grad), _ptr(kpos), _ptr(in_map), _ptr(out_map),
+            in_feats.size(0), out_feats_grad.size(0), kernel_grad.size(1), kernel_grad.size(2), k_vol, dtype, math,
+            _ptr(workspace), workspace.numel() * 4 if workspace is not None else 0, int(bool(accumulate)),
+            _stream()))
+    return workspace
+
+
+def kernel_family(pass_: str, c_in: int, c_out: int, dtype: torch.dtype, arch80: bool = True) -> str:
+    """``"tcgen05"`` or ``"simt"``: which kernel family the dispatch uses for a shape."""
+    d = _lib.DTYPE_F16 if dtype == torch.float16 else _lib.DTYPE_F32
+    m = _lib.MATH_F16 if dtype == torch.float16 else (_lib.MATH_TF32 if arch80 else _lib.MATH_FP32)
+    fam = _L.fgms_b200_kernel_family({"fwd": 0, "dgrad": 1, "wgrad": 2}[pass_], c_in, c_out, d, m)
+    return "tcgen05" if fam == 1 else "simt"
+
+
+def device_status(reset: bool = True) -> int:
+    """Problems kernels reported since the last reset (skipped out-of-range map entries, waits
+    that ran out).  Synchronises the current device."""
+    v = _L.fgms_b200_device_status(int(reset))
+    if v < 0:
+        _lib.check(int(v))
+    return int(v)
+
+
+def launch_count() -> int:
+    return int(_L.fgms_b200_launch_count())

@@ -1,0 +1,145 @@
+// Shared device-side pieces of the fgms_b200 kernels: the parameter block, the per-CTA tile
+// table derived from `kpos`, bounds-checked map reads and the scatter-add primitives.
+#pragma once
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fgms {
+
+// Number of problems kernels ran into (map entries out of range that were skipped, bounded
+// waits that gave up).  Read and reset from the host through fgms_b200_device_status().
+__device__ unsigned long long g_device_problems = 0ull;
+
+__device__ __forceinline__ void report_problem() { atomicAdd(&g_device_problems, 1ull); }
+
+// One gather -> GEMM -> scatter pass.  Forward and dgrad are the same pass with the two maps
+// and the two channel counts exchanged and the weight matrix read transposed; the reference
+// makes the same observation by passing its maps swapped (backend/spconv.cu:460).
+struct GmsParams {
+  const void* src;             // [n_gather , k_dim]  rows that are gathered
+  const void* weights;         // [k_vol, c_in, c_out]
+  void* dst;                   // [n_scatter, n_dim]  rows that are accumulated into
+  const int32_t* kpos;         // [k_vol + 1]
+  const int32_t* gather_map;   // [pairs]
+  const int32_t* scatter_map;  // [pairs]
+  int n_gather, n_scatter;
+  int k_dim, n_dim;            // contraction width, output width
+  int c_in, c_out;             // layout of `weights`
+  int k_vol;
+  int dense_rows;              // > 0: one more segment of `dense_rows` identity pairs ...
+  int dense_weight;            // ... that uses this weight index (the "separate mid" term)
+};
+
+struct WgradParams {
+  const void* feats;     // [n_in , c_in ]
+  const void* out_grad;  // [n_out, c_out]
+  float* dw;             // [k_vol, c_in, c_out] fp32 accumulator
+  const int32_t* kpos;
+  const int32_t* in_map;
+  const int32_t* out_map;
+  int n_in, n_out, c_in, c_out, k_vol;
+};
+
+// ---------------------------------------------------------------------------------------------
+// Tile table.  Segment s < k_vol holds the pairs kpos[s] .. kpos[s+1] of kernel offset s; the
+// optional last segment holds the identity pairs of the dense centre term.  Every segment is cut
+// into tiles of TILE pairs that never straddle two segments — the property the reference gets by
+// padding each offset to a multiple of 256 rows on the host (kpos_quantized, cpu-check.py:6-14)
+// and searching the padded prefix sums per block (backend/utils.cuh:6-27).  Here each CTA derives
+// the table from the unpadded `kpos` itself, so no padded rows are ever scheduled.
+// ---------------------------------------------------------------------------------------------
+template <int TILE>
+__device__ __forceinline__ void build_tile_table(const int32_t* __restrict__ kpos, int k_vol,
+                                                 int dense_rows, int* tile_start /* [k_vol+2] */) {
+  // counts first (parallel), then one thread does the short prefix sum
+  for (int s = threadIdx.x; s <= k_vol; s += blockDim.x) {
+    int cnt = (s < k_vol) ? (__ldg(kpos + s + 1) - __ldg(kpos + s)) : dense_rows;
+    if (cnt < 0) cnt = 0;
+    tile_start[s + 1] = (cnt + TILE - 1) / TILE;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    tile_start[0] = 0;
+    int run = 0;
+    for (int s = 0; s <= k_vol; ++s) {
+      run += tile_start[s + 1];
+      tile_start[s + 1] = run;
+    }
+  }
+  __syncthreads();
+}
+
+// Segment that owns tile t (tile_start is non-decreasing; empty segments are skipped).
+__device__ __forceinline__ int find_segment(const int* tile_start, int n_seg, int t) {
+  int lo = 0, hi = n_seg;  // invariant: tile_start[lo] <= t < tile_start[hi]
+  while (hi - lo > 1) {
+    int mid = (lo + hi) >> 1;
+    if (tile_start[mid] <= t) lo = mid; else hi = mid;
+  }
+  return lo;
+}
+
+// Contiguous share of `total` tiles for this CTA.
+__device__ __forceinline__ void cta_tile_range(int total, int* t0, int* t1) {
+  long long g = gridDim.x, b = blockIdx.x;
+  *t0 = (int)((long long)total * b / g);
+  *t1 = (int)((long long)total * (b + 1) / g);
+}
+
+// ---------------------------------------------------------------------------------------------
+// element helpers
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float to_float(float v) { return v; }
+__device__ __forceinline__ float to_float(__half v) { return __half2float(v); }
+
+__device__ __forceinline__ void red_add(float* p, float v) { atomicAdd(p, v); }
+__device__ __forceinline__ void red_add(__half* p, float v) { atomicAdd(p, __float2half_rn(v)); }
+
+__device__ __forceinline__ void red_add_v4(float* p, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
+}
+__device__ __forceinline__ uint32_t pack_half2(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ void red_add_h2(__half* p, float a, float b) {
+  uint32_t v = pack_half2(a, b);
+  asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_h8(__half* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c),
+               "r"(d)
+               : "memory");
+}
+
+// Add v[0..n) to consecutive elements starting at p.  `vec` says that p is suitably aligned
+// (16 bytes for float4, 4 bytes for half2) — decided once per launch from the channel count.
+template <int N>
+__device__ __forceinline__ void scatter_add(float* p, const float (&v)[N], int valid, bool vec) {
+  if (N == 4 && vec && valid == 4) {
+    red_add_v4(p, v[0], v[1], v[2], v[3]);
+  } else {
+#pragma unroll
+    for (int c = 0; c < N; ++c)
+      if (c < valid) red_add(p + c, v[c]);
+  }
+}
+template <int N>
+__device__ __forceinline__ void scatter_add(__half* p, const float (&v)[N], int valid, bool vec) {
+  if (N % 2 == 0 && vec) {
+#pragma unroll
+    for (int c = 0; c < N; c += 2) {
+      if (c + 1 < valid) red_add_h2(p + c, v[c], v[c + 1]);
+      else if (c < valid) red_add(p + c, v[c]);
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < N; ++c)
+      if (c < valid) red_add(p + c, v[c]);
+  }
+}
+
+}  // namespace fgms

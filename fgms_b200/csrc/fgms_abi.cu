@@ -1,0 +1,333 @@
+// C ABI and host dispatch of fgms_b200 (see include/fgms_b200.h for the contract of every entry
+// point and the reference function each one replaces).  The dispatch plays the role of
+// backend/spconv.cu in the reference: it turns (dtype, math, channel counts) into a kernel choice
+// and a launch; unlike the reference it validates its arguments, launches on the caller's stream
+// and checks the launch status.
+#include "../../include/fgms_b200.h"
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+
+#include "common.cuh"
+#include "simt_kernels.cuh"
+#ifndef FGMS_NO_UMMA
+#include "umma_kernels.cuh"
+#endif
+
+namespace {
+
+thread_local char g_err[512] = "";
+std::atomic<long long> g_launches{0};
+
+int fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_err, sizeof(g_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  return FGMS_OK;
+}
+
+struct DeviceInfo {
+  int sms = 0;
+  int max_smem_optin = 0;
+};
+
+int device_info(DeviceInfo* out) {
+  static thread_local int cached_dev = -1;
+  static thread_local DeviceInfo cached;
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev != cached_dev) {
+    cudaDeviceProp prop;
+    e = cudaGetDeviceProperties(&prop, dev);
+    if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaGetDeviceProperties: %s", cudaGetErrorString(e));
+    cached.sms = prop.multiProcessorCount;
+    cached.max_smem_optin = (int)prop.sharedMemPerBlockOptin;
+    cached_dev = dev;
+  }
+  *out = cached;
+  return FGMS_OK;
+}
+
+bool dtype_ok(int dtype) { return dtype == FGMS_DTYPE_F32 || dtype == FGMS_DTYPE_F16; }
+
+int check_math(int dtype, int math) {
+  if (!dtype_ok(dtype)) return fail(FGMS_ERR_INVALID_ARG, "unknown dtype %d", dtype);
+  if (math != FGMS_MATH_FP32 && math != FGMS_MATH_TF32 && math != FGMS_MATH_F16)
+    return fail(FGMS_ERR_INVALID_ARG, "unknown math mode %d", math);
+  if (math == FGMS_MATH_TF32 && dtype != FGMS_DTYPE_F32)
+    return fail(FGMS_ERR_UNSUPPORTED, "tf32 math needs fp32 storage");
+  if (math == FGMS_MATH_F16 && dtype != FGMS_DTYPE_F16)
+    return fail(FGMS_ERR_UNSUPPORTED, "f16 math needs fp16 storage");
+  return FGMS_OK;
+}
+
+int check_dims(int n_in, int n_out, int c_in, int c_out, int k_vol) {
+  if (n_in < 0 || n_out < 0) return fail(FGMS_ERR_INVALID_ARG, "negative row count");
+  if (c_in < 1 || c_out < 1) return fail(FGMS_ERR_INVALID_ARG, "channel counts must be >= 1");
+  if (k_vol < 1 || k_vol > 4096) return fail(FGMS_ERR_INVALID_ARG, "k_vol %d outside [1, 4096]", k_vol);
+  if ((long long)k_vol * c_in * c_out >= (1ll << 31)) return fail(FGMS_ERR_INVALID_ARG, "weight tensor too large");
+  return FGMS_OK;
+}
+
+// tcgen05 kernels cover rows that are whole 128-byte swizzle spans on both sides
+bool umma_shape_ok(int c_in, int c_out, int dtype) {
+#ifdef FGMS_NO_UMMA
+  (void)c_in; (void)c_out; (void)dtype;
+  return false;
+#else
+  return fgms::umma_supported(c_in, c_out, dtype == FGMS_DTYPE_F16 ? 2 : 4);
+#endif
+}
+
+bool use_umma(int c_in, int c_out, int dtype, int math) {
+  return math != FGMS_MATH_FP32 && umma_shape_ok(c_in, c_out, dtype);
+}
+
+template <typename T, bool TRANS>
+int launch_simt_gms(const fgms::GmsParams& p, cudaStream_t st, int sms) {
+  const size_t dyn = (size_t)(p.k_vol + 2) * sizeof(int);
+  const int grid = sms * 4;
+  if (p.n_dim <= 16) fgms::simt_gms_kernel<T, TRANS, 1><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
+  else fgms::simt_gms_kernel<T, TRANS, 4><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
+  return check_launch("simt_gms_kernel");
+}
+
+// One gather-GEMM-scatter pass (forward when !trans, dgrad when trans).
+int run_gms(bool trans, const void* src, const void* kernel, void* dst, const int32_t* kpos,
+            const int32_t* gather_map, const int32_t* scatter_map, int n_gather, int n_scatter,
+            int c_in, int c_out, int k_vol, int dtype, int math, int dense_rows, int dense_weight,
+            cudaStream_t st) {
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  fgms::GmsParams p;
+  p.src = src; p.weights = kernel; p.dst = dst; p.kpos = kpos;
+  p.gather_map = gather_map; p.scatter_map = scatter_map;
+  p.n_gather = n_gather; p.n_scatter = n_scatter;
+  p.k_dim = trans ? c_out : c_in;
+  p.n_dim = trans ? c_in : c_out;
+  p.c_in = c_in; p.c_out = c_out; p.k_vol = k_vol;
+  p.dense_rows = dense_rows; p.dense_weight = dense_weight;
+#ifndef FGMS_NO_UMMA
+  if (use_umma(c_in, c_out, dtype, math)) {
+    int rc = fgms::launch_umma_gms(p, trans, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
+    if (rc == 0) return check_launch("umma_gms_kernel");
+    if (rc < 0) return fail(FGMS_ERR_CUDA, "umma_gms_kernel setup failed (%d)", rc);
+    // rc > 0: shape does not fit the tensor-core kernel's shared memory; take the CUDA-core path
+  }
+#endif
+  if (dtype == FGMS_DTYPE_F16)
+    return trans ? launch_simt_gms<__half, true>(p, st, di.sms) : launch_simt_gms<__half, false>(p, st, di.sms);
+  return trans ? launch_simt_gms<float, true>(p, st, di.sms) : launch_simt_gms<float, false>(p, st, di.sms);
+}
+
+int mid_offset(int k_vol) { return (k_vol % 2 == 1) ? k_vol / 2 : 0; }
+
+int check_fwd_args(const void* in_feats, const void* kernel, void* out_feats, const int32_t* kpos,
+                   const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
+                   int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                   int separate_mid) {
+  if (c_in != kernel_c_in)
+    return fail(FGMS_ERR_CHANNEL_MISMATCH, "Input feature size and kernel size mismatch");
+  if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
+  if (int rc = check_math(dtype, math)) return rc;
+  if (!kernel || !kpos) return fail(FGMS_ERR_INVALID_ARG, "kernel / kpos must not be null");
+  if ((n_in > 0 && !in_feats) || (n_out > 0 && !out_feats)) return fail(FGMS_ERR_INVALID_ARG, "feature pointer is null");
+  if (sum_nnz < 0) return fail(FGMS_ERR_INVALID_ARG, "sum_nnz is negative");
+  if (sum_nnz > 0 && (!in_map || !out_map)) return fail(FGMS_ERR_INVALID_ARG, "map pointer is null");
+  if (separate_mid && n_in != n_out)
+    return fail(FGMS_ERR_INVALID_ARG, "separate_mid needs n_in == n_out (got %d, %d)", n_in, n_out);
+  return FGMS_OK;
+}
+
+size_t elem_size(int dtype) { return dtype == FGMS_DTYPE_F16 ? 2 : 4; }
+
+}  // namespace
+
+extern "C" {
+
+int fgms_b200_fusion_fwd(const void* in_feats, const void* kernel, void* out_feats,
+                         const int32_t* kpos, const int32_t* qkpos, const int32_t* in_map,
+                         const int32_t* out_map, int n_in, int n_out, int c_in, int kernel_c_in,
+                         int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                         int separate_mid, void* stream) {
+  (void)qkpos;
+  if (int rc = check_fwd_args(in_feats, kernel, out_feats, kpos, in_map, out_map, n_in, n_out, c_in,
+                              kernel_c_in, c_out, k_vol, sum_nnz, dtype, math, separate_mid))
+    return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (separate_mid && n_out > 0) {
+    // the reference's centre GEMM runs first with beta = 0: previous contents are discarded
+    cudaError_t e = cudaMemsetAsync(out_feats, 0, (size_t)n_out * c_out * elem_size(dtype), st);
+    if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  }
+  return run_gms(false, in_feats, kernel, out_feats, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
+                 k_vol, dtype, math, separate_mid ? n_in : 0, mid_offset(k_vol), st);
+}
+
+int fgms_b200_seq_fwd(const void* in_feats, const void* kernel, void* out_feats,
+                      const int32_t* kernel_nnz_host, const int32_t* kpos, const int32_t* in_map,
+                      const int32_t* out_map, int n_in, int n_out, int c_in, int kernel_c_in,
+                      int c_out, int k_vol, int64_t sum_nnz, int dtype, int math, int separate_mid,
+                      void* stream) {
+  if (int rc = check_fwd_args(in_feats, kernel, out_feats, kpos, in_map, out_map, n_in, n_out, c_in,
+                              kernel_c_in, c_out, k_vol, sum_nnz, dtype, math, separate_mid))
+    return rc;
+  if (!kernel_nnz_host) return fail(FGMS_ERR_INVALID_ARG, "kernel_nnz (host) must not be null");
+  long long total = 0;
+  for (int k = 0; k < k_vol; ++k) {
+    if (kernel_nnz_host[k] < 0) return fail(FGMS_ERR_INVALID_ARG, "kernel_nnz[%d] is negative", k);
+    total += kernel_nnz_host[k];
+  }
+  if (total != sum_nnz)
+    return fail(FGMS_ERR_INVALID_ARG, "kernel_nnz sums to %lld but sum_nnz is %lld", total, (long long)sum_nnz);
+  return run_gms(false, in_feats, kernel, out_feats, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
+                 k_vol, dtype, math, separate_mid ? n_in : 0, mid_offset(k_vol),
+                 static_cast<cudaStream_t>(stream));
+}
+
+int fgms_b200_dgrad(const void* out_grad, const void* kernel, void* in_grad, const int32_t* kpos,
+                    const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
+                    int c_out, int k_vol, int dtype, int math, void* stream) {
+  if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
+  if (int rc = check_math(dtype, math)) return rc;
+  if (!kernel || !kpos) return fail(FGMS_ERR_INVALID_ARG, "kernel / kpos must not be null");
+  if ((n_out > 0 && !out_grad) || (n_in > 0 && !in_grad)) return fail(FGMS_ERR_INVALID_ARG, "gradient pointer is null");
+  return run_gms(true, out_grad, kernel, in_grad, kpos, out_map, in_map, n_out, n_in, c_in, c_out, k_vol,
+                 dtype, math, 0, 0, static_cast<cudaStream_t>(stream));
+}
+
+size_t fgms_b200_wgrad_workspace_bytes(int c_in, int c_out, int k_vol, int dtype) {
+  if (dtype != FGMS_DTYPE_F16 || c_in < 1 || c_out < 1 || k_vol < 1) return 0;
+  return (size_t)k_vol * c_in * c_out * sizeof(float);
+}
+
+int fgms_b200_wgrad_finalize(void* kernel_grad_f16, const void* workspace_f32, int64_t count, void* stream) {
+  if (count < 0) return fail(FGMS_ERR_INVALID_ARG, "negative count");
+  if (count == 0) return FGMS_OK;
+  if (!kernel_grad_f16 || !workspace_f32) return fail(FGMS_ERR_INVALID_ARG, "null pointer");
+  int blocks = (int)((count + 255) / 256);
+  if (blocks > 1184) blocks = 1184;
+  fgms::wgrad_finalize_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__half*>(kernel_grad_f16), static_cast<const float*>(workspace_f32), (long long)count);
+  return check_launch("wgrad_finalize_kernel");
+}
+
+int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_grad,
+                    const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in,
+                    int n_out, int c_in, int c_out, int k_vol, int dtype, int math, void* workspace,
+                    size_t workspace_bytes, int accumulate_into_kernel_grad, void* stream) {
+  if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
+  if (int rc = check_math(dtype, math)) return rc;
+  if (!kpos) return fail(FGMS_ERR_INVALID_ARG, "kpos must not be null");
+  if ((n_in > 0 && !in_feats) || (n_out > 0 && !out_grad)) return fail(FGMS_ERR_INVALID_ARG, "feature pointer is null");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  const size_t count = (size_t)k_vol * c_in * c_out;
+
+  float* acc = nullptr;
+  if (dtype == FGMS_DTYPE_F16) {
+    const size_t need = fgms_b200_wgrad_workspace_bytes(c_in, c_out, k_vol, dtype);
+    if (!workspace || workspace_bytes < need)
+      return fail(FGMS_ERR_WORKSPACE, "wgrad needs a %zu-byte workspace for fp16 storage (got %zu)", need,
+                  workspace ? workspace_bytes : (size_t)0);
+    if (reinterpret_cast<uintptr_t>(workspace) & 255)
+      return fail(FGMS_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+    if (accumulate_into_kernel_grad && !kernel_grad) return fail(FGMS_ERR_INVALID_ARG, "kernel_grad is null");
+    cudaError_t e = cudaMemsetAsync(workspace, 0, need, st);
+    if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+    acc = static_cast<float*>(workspace);
+  } else {
+    if (!kernel_grad) return fail(FGMS_ERR_INVALID_ARG, "kernel_grad is null");
+    acc = static_cast<float*>(kernel_grad);
+  }
+
+  fgms::WgradParams p;
+  p.feats = in_feats; p.out_grad = out_grad; p.dw = acc; p.kpos = kpos;
+  p.in_map = in_map; p.out_map = out_map;
+  p.n_in = n_in; p.n_out = n_out; p.c_in = c_in; p.c_out = c_out; p.k_vol = k_vol;
+
+  bool launched = false;
+#ifndef FGMS_NO_UMMA
+  if (use_umma(c_in, c_out, dtype, math)) {
+    int rc = fgms::launch_umma_wgrad(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
+    if (rc == 0) {
+      if (int rc2 = check_launch("umma_wgrad_kernel")) return rc2;
+      launched = true;
+    } else if (rc < 0) {
+      return fail(FGMS_ERR_CUDA, "umma_wgrad_kernel setup failed (%d)", rc);
+    }
+  }
+#endif
+  if (!launched) {
+    const size_t dyn = (size_t)(k_vol + 2) * sizeof(int);
+    const int grid = di.sms * 4;
+    const bool small = c_in <= 16 && c_out <= 16;
+    if (dtype == FGMS_DTYPE_F16) {
+      if (small) fgms::simt_wgrad_kernel<__half, 1><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
+      else fgms::simt_wgrad_kernel<__half, 4><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
+    } else {
+      if (small) fgms::simt_wgrad_kernel<float, 1><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
+      else fgms::simt_wgrad_kernel<float, 4><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
+    }
+    if (int rc = check_launch("simt_wgrad_kernel")) return rc;
+  }
+  if (dtype == FGMS_DTYPE_F16 && accumulate_into_kernel_grad)
+    return fgms_b200_wgrad_finalize(kernel_grad, workspace, (int64_t)count, stream);
+  return FGMS_OK;
+}
+
+int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel, void* in_grad,
+                  void* kernel_grad, const int32_t* kpos, const int32_t* qkpos,
+                  const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
+                  int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                  int separate_mid, void* workspace, size_t workspace_bytes, void* stream) {
+  (void)qkpos; (void)separate_mid;
+  if (c_in != kernel_c_in)
+    return fail(FGMS_ERR_CHANNEL_MISMATCH, "Input feature size and kernel size mismatch");
+  if (sum_nnz < 0) return fail(FGMS_ERR_INVALID_ARG, "sum_nnz is negative");
+  if (sum_nnz > 0 && (!in_map || !out_map)) return fail(FGMS_ERR_INVALID_ARG, "map pointer is null");
+  if (int rc = fgms_b200_dgrad(out_grad, kernel, in_grad, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
+                               k_vol, dtype, math, stream))
+    return rc;
+  return fgms_b200_wgrad(in_feats, out_grad, kernel_grad, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
+                         k_vol, dtype, math, workspace, workspace_bytes, 1, stream);
+}
+
+int fgms_b200_kernel_family(int pass, int c_in, int c_out, int dtype, int math) {
+  if (pass < 0 || pass > 2 || !dtype_ok(dtype)) return fail(FGMS_ERR_INVALID_ARG, "bad pass or dtype");
+  return use_umma(c_in, c_out, dtype, math) ? 1 : 0;
+}
+
+int64_t fgms_b200_device_status(int reset) {
+  cudaError_t e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaDeviceSynchronize: %s", cudaGetErrorString(e));
+  unsigned long long v = 0;
+  e = cudaMemcpyFromSymbol(&v, fgms::g_device_problems, sizeof(v));
+  if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaMemcpyFromSymbol: %s", cudaGetErrorString(e));
+  if (reset) {
+    unsigned long long z = 0;
+    e = cudaMemcpyToSymbol(fgms::g_device_problems, &z, sizeof(z));
+    if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaMemcpyToSymbol: %s", cudaGetErrorString(e));
+  }
+  return (int64_t)v;
+}
+
+int64_t fgms_b200_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+const char* fgms_b200_last_error(void) { return g_err; }
+
+const char* fgms_b200_version(void) { return "fgms_b200 0.1 (sm_100a)"; }
+
+}  // extern "C"

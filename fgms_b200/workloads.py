@@ -1,0 +1,80 @@
+"""Named benchmark workloads: the synthetic stand-ins for the reference's sample layers.
+
+Each workload is one sparse-convolution layer (cloud → kernel map, channel counts, arithmetic
+mode).  The clouds are seeded, so the exact voxel and pair counts are reproducible; they are
+recorded with every result.
+
+================  =====================================================================
+``cfg1``          8 000 voxels uniform in 64^3, 3x3x3 submanifold, fp32 16→16
+``cfg2``          ~100 k-voxel indoor-surface cloud in 256^3, 3x3x3 submanifold, fp16 64→64
+``cfg3a``         ~200 k-voxel surface cloud in 512^3, 2x2x2 stride-2 downsample, tf32 32→64
+``cfg3b``         the transposed 2x2x2 convolution back to the fine voxels, tf32 64→32
+``cfg4``          two overlaid 64-beam LiDAR sweeps voxelised at 5 cm (~145 k voxels),
+                  3x3x3 submanifold, fp16 128→128
+================  =====================================================================
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from functools import lru_cache
+
+from . import clouds, maps
+
+__all__ = ["Workload", "get", "NAMES", "flops", "algorithmic_bytes"]
+
+NAMES = ("cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4")
+
+
+@dataclass(frozen=True)
+class Workload:
+    name: str
+    description: str
+    kmap: maps.KernelMap
+    c_in: int
+    c_out: int
+    mode: str  # "fp32" | "tf32" | "fp16"
+    seed: int
+
+    @property
+    def elem_bytes(self) -> int:
+        return 2 if self.mode == "fp16" else 4
+
+
+@lru_cache(maxsize=None)
+def get(name: str, seed_offset: int = 0) -> Workload:
+    """Build (and cache) a workload.  ``seed_offset`` gives an independent scene of the same
+    kind — one per rank in multi-GPU runs."""
+    s = seed_offset
+    if name == "cfg1":
+        km = maps.build_submanifold_map(clouds.uniform_cloud(8000, 64, 101 + s))
+        return Workload(name, "uniform 8k voxels in 64^3, subm 3x3x3, fp32 16->16", km, 16, 16, "fp32", 101 + s)
+    if name == "cfg2":
+        km = maps.build_submanifold_map(clouds.surface_cloud(100_000, 256, 102 + s))
+        return Workload(name, "indoor-surface ~100k voxels in 256^3, subm 3x3x3, fp16 64->64", km, 64, 64, "fp16", 102 + s)
+    if name in ("cfg3a", "cfg3b"):
+        coords = clouds.surface_cloud(200_000, 512, 103 + s)
+        down = maps.build_strided_map(coords, 2, 2)
+        if name == "cfg3a":
+            return Workload(name, "surface ~200k voxels in 512^3, 2x2x2 stride 2, tf32 32->64", down, 32, 64, "tf32", 103 + s)
+        up = maps.transpose_map(down, coords)
+        return Workload(name, "transposed 2x2x2 back to ~200k voxels, tf32 64->32", up, 64, 32, "tf32", 103 + s)
+    if name == "cfg4":
+        km = maps.build_submanifold_map(clouds.lidar_cloud(104 + s, sweeps=2))
+        return Workload(name, "64-beam LiDAR, 2 sweeps, 5 cm voxels (~145k), subm 3x3x3, fp16 128->128", km, 128, 128, "fp16", 104 + s)
+    raise KeyError(name)
+
+
+def flops(wl: Workload, passes: int = 3) -> float:
+    """Effective flops: 2 * pairs * c_in * c_out per pass (forward, dgrad, wgrad)."""
+    return 2.0 * wl.kmap.pairs * wl.c_in * wl.c_out * passes
+
+
+def algorithmic_bytes(wl: Workload, which: str) -> float:
+    """Algorithmic bytes of one pass under the gathered-bytes model: every pair reads one
+    gathered row and updates one scattered row, both maps are read once, weights once.
+    ``which``: "fwd" | "dgrad" | "wgrad" | "all"."""
+    p, s = wl.kmap.pairs, wl.elem_bytes
+    w_elems = wl.kmap.k_vol * wl.c_in * wl.c_out
+    gms = p * (wl.c_in + wl.c_out) * s + 8 * p + w_elems * s
+    wg = p * (wl.c_in + wl.c_out) * s + 8 * p + w_elems * 4
+    return {"fwd": gms, "dgrad": gms, "wgrad": wg, "all": 2 * gms + wg}[which]

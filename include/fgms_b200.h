@@ -1,0 +1,134 @@
+/*
+ * fgms_b200 — C ABI of the B200-native sparse-convolution backend.
+ *
+ * Drop-in boundary for the operator surface of hkeee21/FGMS (backend/pybind_cuda.cpp:7-11,
+ * prototypes backend/spconv.h:10-49).  The reference binds three C++ functions that take
+ * at::Tensor handles; this library exposes the same three operations on plain device
+ * pointers and sizes, so that any binding layer (ctypes, pybind11, cgo, JNI ...) can call
+ * them without linking PyTorch.  All pointers are DEVICE pointers unless a parameter says
+ * otherwise; all matrices are dense row-major and contiguous.
+ *
+ *   in_feats   [n_in , c_in ]             features of the input voxels
+ *   kernel     [k_vol, c_in, c_out]       one weight matrix per kernel offset
+ *   out_feats  [n_out, c_out]             accumulated into (caller zeroes it)
+ *   kpos       int32 [k_vol + 1]          start of each offset's slice of the maps
+ *   in_map / out_map  int32 [kpos[k_vol]] flat, offset-major (input row, output row) pairs
+ *
+ * Every function returns FGMS_OK (0) or a negative FGMS_ERR_* code and never throws; the
+ * text of the last error of the calling thread is available from fgms_b200_last_error().
+ * Kernels are enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default
+ * stream, which is what the reference always uses, backend/spconv.cu:73) and the call
+ * returns without synchronising, like the reference.
+ */
+#ifndef FGMS_B200_H_
+#define FGMS_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FGMS_OK 0
+#define FGMS_ERR_INVALID_ARG (-1)      /* null pointer, negative size, unknown enum */
+#define FGMS_ERR_CHANNEL_MISMATCH (-2) /* "Input feature size and kernel size mismatch" (backend/spconv.cu:39-43) */
+#define FGMS_ERR_UNSUPPORTED (-3)      /* dtype/math combination that does not exist */
+#define FGMS_ERR_CUDA (-4)             /* a CUDA runtime call or launch failed */
+#define FGMS_ERR_WORKSPACE (-5)        /* workspace missing or too small */
+#define FGMS_ERR_DEVICE (-6)           /* a kernel reported a problem (bad map index, wait limit hit) */
+
+/* storage type of in_feats / kernel / out_feats (the reference decides on in_feats.scalar_type(),
+ * backend/spconv.cu:47-48) */
+#define FGMS_DTYPE_F32 0
+#define FGMS_DTYPE_F16 1
+
+/* arithmetic of the per-offset contraction.  Accumulation is always fp32.
+ *   FP32 : CUDA-core FFMA on the stored values (fp16 storage is widened exactly) — the
+ *          reference's arch80 == false fp32 path (backend/spconv.cu:221-228); also the path taken
+ *          for channel counts the tensor-core kernels do not cover.
+ *   TF32 : tcgen05 kind::tf32 on fp32 storage — the reference's arch80 == true fp32 path
+ *          (backend/spconv.cu:213-220, wmma m16n16k8 there).
+ *   F16  : tcgen05 kind::f16 on fp16 storage — the reference's fp16 path
+ *          (backend/spconv.cu:108-201, wmma m16n16k16 with fp16 accumulators there). */
+#define FGMS_MATH_FP32 0
+#define FGMS_MATH_TF32 1
+#define FGMS_MATH_F16 2
+
+/* Fused forward:  out[out_map[j]] += in[in_map[j]] . kernel[k(j)]  for every pair j.
+ * Replaces ConvolutionForwardFused (backend/spconv.cu:23-246; Python name fgms_fusion_fwd_cuda).
+ * `qkpos` (the 256-padded prefix sums of cpu-check.py:6-14) and `sum_nnz` (= qkpos[k_vol]) belong
+ * to the reference's tiling contract; this library tiles from `kpos` alone and accepts
+ * qkpos == NULL.  separate_mid != 0: the centre offset (k_vol/2 for odd k_vol, else 0) is applied
+ * densely to all rows (requires n_in == n_out and maps without centre pairs) and, as in the
+ * reference (beta = 0, backend/spconv.cu:55-56,76-106), out_feats is OVERWRITTEN, not accumulated. */
+int fgms_b200_fusion_fwd(const void* in_feats, const void* kernel, void* out_feats,
+                         const int32_t* kpos, const int32_t* qkpos, const int32_t* in_map,
+                         const int32_t* out_map, int n_in, int n_out, int c_in, int kernel_c_in,
+                         int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                         int separate_mid, void* stream);
+
+/* Per-offset ("sequential") forward.  Replaces ConvolutionForward (backend/spconv.cu:249-411;
+ * Python name fgms_fwd_cuda).  `kernel_nnz_host` is a HOST array of k_vol counts, as in the
+ * reference (backend/spconv.cu:308); it is checked against sum_nnz and otherwise unused because
+ * the same single-launch kernel runs.  separate_mid adds the dense centre term to out_feats
+ * (beta = 1, backend/spconv.cu:282-283,378-410) without overwriting. */
+int fgms_b200_seq_fwd(const void* in_feats, const void* kernel, void* out_feats,
+                      const int32_t* kernel_nnz_host, const int32_t* kpos, const int32_t* in_map,
+                      const int32_t* out_map, int n_in, int n_out, int c_in, int kernel_c_in,
+                      int c_out, int k_vol, int64_t sum_nnz, int dtype, int math, int separate_mid,
+                      void* stream);
+
+/* Input gradient:  in_grad[in_map[j]] += out_grad[out_map[j]] . kernel[k(j)]^T.
+ * First launch of ConvolutionBackward (backend/spconv.cu:454-461 fp16, 553-560 tf32). */
+int fgms_b200_dgrad(const void* out_grad, const void* kernel, void* in_grad, const int32_t* kpos,
+                    const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
+                    int c_out, int k_vol, int dtype, int math, void* stream);
+
+/* Weight gradient:  kernel_grad[k] += sum over the pairs of offset k of in[in_map[j]]^T (x) out_grad[out_map[j]].
+ * Second launch of ConvolutionBackward (backend/spconv.cu:495-548 fp16, 562-569 tf32).
+ * Partial sums are accumulated in fp32.  For fp16 storage they live in `workspace`
+ * (>= fgms_b200_wgrad_workspace_bytes() bytes, 256-byte aligned device memory, contents
+ * ignored on entry; on return it holds the fp32 [k_vol, c_in, c_out] gradient of THIS call, which
+ * is what a multi-GPU caller all-reduces) and are then added to kernel_grad; for fp32 storage
+ * workspace may be NULL and kernel_grad is accumulated directly.
+ * accumulate_into_kernel_grad == 0 leaves kernel_grad untouched (fp16 only): the caller reduces
+ * the workspace across ranks and calls fgms_b200_wgrad_finalize itself. */
+int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_grad,
+                    const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in,
+                    int n_out, int c_in, int c_out, int k_vol, int dtype, int math, void* workspace,
+                    size_t workspace_bytes, int accumulate_into_kernel_grad, void* stream);
+
+/* kernel_grad (fp16) += workspace (fp32), element-wise over k_vol * c_in * c_out values. */
+int fgms_b200_wgrad_finalize(void* kernel_grad_f16, const void* workspace_f32, int64_t count,
+                             void* stream);
+
+size_t fgms_b200_wgrad_workspace_bytes(int c_in, int c_out, int k_vol, int dtype);
+
+/* Both gradients.  Replaces ConvolutionBackward (backend/spconv.cu:414-571; Python name
+ * fgms_bwd_cuda).  separate_mid is accepted and ignored, as in the reference. */
+int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel, void* in_grad,
+                  void* kernel_grad, const int32_t* kpos, const int32_t* qkpos,
+                  const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
+                  int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                  int separate_mid, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Which kernel family the dispatch picks for a shape: 0 = CUDA-core (SIMT), 1 = tcgen05.
+ * pass: 0 forward, 1 dgrad, 2 wgrad. */
+int fgms_b200_kernel_family(int pass, int c_in, int c_out, int dtype, int math);
+
+/* Device-side problem counter of the current device: number of map entries outside
+ * [0, n_in) / [0, n_out) that kernels skipped plus bounded waits that ran out, since the last
+ * reset.  Synchronises the device.  Returns the count (>= 0) or a negative FGMS_ERR_*. */
+int64_t fgms_b200_device_status(int reset);
+
+/* Number of kernels this library has launched from this process (all threads). */
+int64_t fgms_b200_launch_count(void);
+
+const char* fgms_b200_last_error(void);
+const char* fgms_b200_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FGMS_B200_H_ */

@@ -1,0 +1,83 @@
+"""The C-ABI library: it loads, exports every symbol the header declares, and rejects bad
+arguments before touching a device (these checks run without a GPU)."""
+import ctypes
+import os
+import re
+
+import pytest
+
+from fgms_b200 import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _declared_symbols():
+    names = set()
+    inc = os.path.join(ROOT, "include")
+    for f in os.listdir(inc):
+        if f.endswith(".h"):
+            text = open(os.path.join(inc, f)).read()
+            text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+            names |= set(re.findall(r"\b(fgms_b200_\w+)\s*\(", text))
+    return names
+
+
+def test_library_exports_every_declared_symbol():
+    declared = _declared_symbols()
+    assert len(declared) >= 10
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(raw, name), f"{name} is declared in include/ but not exported"
+    assert declared == set(_lib.SIGNATURES), "ctypes signatures out of step with the header"
+    assert b"sm_100a" in _lib.lib.fgms_b200_version()
+
+
+def test_channel_mismatch_is_the_reference_error():
+    L = _lib.lib
+    rc = L.fgms_b200_fusion_fwd(None, None, None, None, None, None, None, 4, 4, 16, 8, 16, 27, 0, 0, 0, 0, None)
+    assert rc == _lib.ERR_CHANNEL_MISMATCH
+    assert _lib.last_error() == "Input feature size and kernel size mismatch"  # backend/spconv.cu:39-43
+    with pytest.raises(ValueError, match="Input feature size and kernel size mismatch"):
+        _lib.check(rc)
+    rc = L.fgms_b200_bwd(None, None, None, None, None, None, None, None, None, 4, 4, 16, 8, 16, 27, 0, 0, 0, 0, None, 0, None)
+    assert rc == _lib.ERR_CHANNEL_MISMATCH
+
+
+@pytest.mark.parametrize("args,code", [
+    (dict(dtype=7), _lib.ERR_INVALID_ARG),
+    (dict(math=9), _lib.ERR_INVALID_ARG),
+    (dict(dtype=_lib.DTYPE_F16, math=_lib.MATH_TF32), _lib.ERR_UNSUPPORTED),
+    (dict(dtype=_lib.DTYPE_F32, math=_lib.MATH_F16), _lib.ERR_UNSUPPORTED),
+    (dict(k_vol=0), _lib.ERR_INVALID_ARG),
+    (dict(c_out=0), _lib.ERR_INVALID_ARG),
+    (dict(n_in=-1), _lib.ERR_INVALID_ARG),
+    (dict(sum_nnz=-5), _lib.ERR_INVALID_ARG),
+    (dict(separate_mid=1, n_out=5), _lib.ERR_INVALID_ARG),
+    (dict(), _lib.ERR_INVALID_ARG),  # null kernel / kpos
+])
+def test_argument_validation_without_a_device(args, code):
+    a = dict(n_in=4, n_out=4, c_in=8, c_out=8, k_vol=27, sum_nnz=0, dtype=0, math=0, separate_mid=0)
+    a.update(args)
+    rc = _lib.lib.fgms_b200_fusion_fwd(None, None, None, None, None, None, None, a["n_in"], a["n_out"], a["c_in"],
+                                       a["c_in"], a["c_out"], a["k_vol"], a["sum_nnz"], a["dtype"], a["math"],
+                                       a["separate_mid"], None)
+    assert rc == code, _lib.last_error()
+    assert _lib.last_error()
+
+
+def test_workspace_size_and_family_queries():
+    L = _lib.lib
+    assert L.fgms_b200_wgrad_workspace_bytes(128, 128, 27, _lib.DTYPE_F16) == 27 * 128 * 128 * 4
+    assert L.fgms_b200_wgrad_workspace_bytes(128, 128, 27, _lib.DTYPE_F32) == 0
+    assert L.fgms_b200_kernel_family(0, 16, 16, _lib.DTYPE_F32, _lib.MATH_FP32) == 0
+    assert L.fgms_b200_kernel_family(0, 128, 128, _lib.DTYPE_F32, _lib.MATH_FP32) == 0  # fp32 math is never tensor-core
+    assert L.fgms_b200_kernel_family(0, 17, 33, _lib.DTYPE_F16, _lib.MATH_F16) == 0
+    assert L.fgms_b200_launch_count() >= 0
+
+
+def test_seq_forward_checks_host_counts():
+    import numpy as np
+    knnz = np.array([1, 2, 3], dtype=np.int32)
+    one = ctypes.c_void_p(8)  # never dereferenced: validation fails first
+    rc = _lib.lib.fgms_b200_seq_fwd(one, one, one, knnz.ctypes.data, one, one, one, 4, 4, 8, 8, 8, 3, 7, 0, 0, 0, None)
+    assert rc == _lib.ERR_INVALID_ARG and "sums to 6" in _lib.last_error()
