@@ -50,8 +50,7 @@ struct WgradParams {
 // and searching the padded prefix sums per block (backend/utils.cuh:6-27).  Here each CTA derives
 // the table from the unpadded `kpos` itself, so no padded rows are ever scheduled.
 // ---------------------------------------------------------------------------------------------
-template <int TILE>
-__device__ __forceinline__ void build_tile_table(const int32_t* __restrict__ kpos, int k_vol,
+__device__ __forceinline__ void build_tile_table(int TILE, const int32_t* __restrict__ kpos, int k_vol,
                                                  int dense_rows, int* tile_start /* [k_vol+2] */) {
   // counts first (parallel), then one thread does the short prefix sum
   for (int s = threadIdx.x; s <= k_vol; s += blockDim.x) {

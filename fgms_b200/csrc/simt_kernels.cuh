@@ -37,7 +37,7 @@ __global__ void __launch_bounds__(SIMT_THREADS) simt_gms_kernel(GmsParams p) {
   const int tx = tid & 15, ty = tid >> 4;
   const int n_seg = p.k_vol + 1;
 
-  build_tile_table<SIMT_TILE_M>(p.kpos, p.k_vol, p.dense_rows, tile_start);
+  build_tile_table(SIMT_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);
   int t0, t1;
   cta_tile_range(tile_start[n_seg], &t0, &t1);
 
@@ -158,7 +158,7 @@ __global__ void __launch_bounds__(SIMT_THREADS) simt_wgrad_kernel(WgradParams p)
   const int tid = threadIdx.x;
   const int tx = tid & 15, ty = tid >> 4;
   const int n_seg = p.k_vol + 1;
-  build_tile_table<SIMT_WG_TILE>(p.kpos, p.k_vol, 0, tile_start);
+  build_tile_table(SIMT_WG_TILE, p.kpos, p.k_vol, 0, tile_start);
   int t0, t1;
   cta_tile_range(tile_start[n_seg], &t0, &t1);
   const bool vec = (p.c_out % 4 == 0) && (reinterpret_cast<uintptr_t>(p.dw) & 15) == 0;

@@ -36,15 +36,18 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait (about a quarter of a second at the outside).  `abort_flag` (shared memory) lets one
+// Bounded wait: gives up after about one second of SM clock.  `abort_flag` (shared memory) lets one
 // role tell the others to stop waiting once something has gone wrong.
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr long long WAIT_LIMIT_CYCLES = 2000000000ll;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  for (uint32_t it = 0; it < WAIT_LIMIT; ++it) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63) == 63) {
+    if ((it & 31) == 0) {
       if (abort_flag && *abort_flag) return false;
-      __nanosleep(40);
+      if (clock64() - start > WAIT_LIMIT_CYCLES) break;
+      __nanosleep(32);
     }
   }
   if (abort_flag) *abort_flag = 1;
@@ -134,13 +137,14 @@ __host__ __device__ constexpr uint32_t make_idesc(bool tf32, bool a_mn_major, bo
 // Shared-memory matrix descriptor, 128-byte swizzle:
 //   [0,14) start address >> 4   [16,30) leading byte offset >> 4   [32,46) stride byte offset >> 4
 //   [46,48) version = 1 (sm_100)   [61,64) layout type = 2 (SWIZZLE_128B)
-__device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+__device__ __forceinline__ uint64_t make_sdesc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes,
+                                              uint32_t layout_type = 2) {
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)layout_type << 61;
   return d;
 }
 
@@ -161,6 +165,14 @@ __host__ __device__ constexpr uint32_t kmajor_offset(uint32_t row, uint32_t byte
 __host__ __device__ constexpr uint32_t mnmajor_offset(uint32_t k, uint32_t byte_in_row, uint32_t lbo, uint32_t sbo) {
   return (byte_in_row >> 7) * lbo + (k >> 3) * sbo + (k & 7u) * 128u +
          ((((byte_in_row >> 4) & 7u) ^ (k & 7u)) << 4) + (byte_in_row & 15u);
+}
+
+// MN-major for 32-bit elements (tf32) has its own layout, "128-byte swizzle with 32-byte atomicity"
+// (descriptor layout type 1): atoms are 4 consecutive k (512 bytes), and the 32-byte chunk q of row k
+// sits at chunk position q ^ (k % 4).  `sbo` is the distance between atoms that follow each other in k.
+__host__ __device__ constexpr uint32_t mnmajor32_offset(uint32_t k, uint32_t byte_in_row, uint32_t lbo, uint32_t sbo) {
+  return (byte_in_row >> 7) * lbo + (k >> 2) * sbo + (k & 3u) * 128u +
+         ((((byte_in_row >> 5) & 3u) ^ (k & 3u)) << 5) + (byte_in_row & 31u);
 }
 
 }  // namespace umma

@@ -1,0 +1,620 @@
+// Tensor-core kernels for sm_100a: gather -> tcgen05.mma (accumulators in tensor memory) -> scatter.
+//
+// Both kernels are persistent (one CTA per SM, each walking a contiguous share of the tile list
+// derived from `kpos`) and warp-specialised:
+//
+//   warps 0-3  epilogue   tcgen05.ld of the fp32 accumulators, conversion, vector red.global.add
+//   warp  4    MMA        one thread issues tcgen05.mma / tcgen05.commit; owns the TMEM allocation
+//   warps 5-8  producers  gather rows with 16-byte cp.async straight into the 128-byte-swizzled
+//                         operand layout tcgen05 reads (no staging copy, no register round trip)
+//
+// Shared-memory stages and the two TMEM accumulator buffers are handed between the roles with
+// mbarriers; every wait is bounded (umma::mbar_wait) and a wait that runs out makes all roles leave
+// their loops, reports a problem and still frees the tensor memory.
+//
+// What these kernels replace in the reference: the wmma forward kernels (backend/fwd_kernels.cuh:17-144,
+// backend/spconv.cuh:1328-1477, 1634-1776), the dgrad kernels (backend/bwd_kernels.cuh:13-142, 281-408)
+// and the wgrad kernels (backend/bwd_kernels.cuh:419-527, 876-1368).  Differences that matter: a tile's
+// gathered rows are loaded once and multiplied against the full output width (the reference re-gathers
+// per 32 output columns, and wgrad per 32x32 weight tile), accumulation is fp32 for fp16 data, tiles
+// come from the unpadded `kpos`, and every access is bounds-checked.
+#pragma once
+
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace fgms {
+
+constexpr int UMMA_THREADS = 288;
+constexpr int UMMA_PROD_THREADS = 128;
+constexpr int UMMA_PROD_TID0 = 160;
+constexpr int UMMA_TILE_M = 128;      // pairs per forward / dgrad tile
+constexpr int UMMA_STAGE_BYTES = 16384;
+constexpr int UMMA_MAX_STAGES = 8;
+constexpr int UMMA_LOOKAHEAD = 3;     // cp.async groups a producer thread keeps in flight
+constexpr int UMMA_SMEM_FIXED = 1024 /* alignment slack */ + 512 /* barriers, flags */;
+
+// shapes the tensor-core kernels take: both channel counts fill whole 128-byte spans, at most 256
+inline bool umma_supported(int c_in, int c_out, int elem_bytes) {
+  return (c_in * elem_bytes) % 128 == 0 && (c_out * elem_bytes) % 128 == 0 && c_in <= 256 && c_out <= 256;
+}
+
+struct UmmaShared {
+  uint64_t full[UMMA_MAX_STAGES];
+  uint64_t empty[UMMA_MAX_STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static_assert(sizeof(UmmaShared) <= 256, "barrier block must fit its slot");
+
+__device__ __forceinline__ uint8_t* align_1024(uint8_t* p) {
+  return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
+}
+
+__device__ __forceinline__ uint32_t tmem_cols_pow2(uint32_t need) {
+  uint32_t c = 32;
+  while (c < need) c <<= 1;
+  return c;
+}
+
+// =============================================================================================
+// forward / dgrad
+//   A = gathered rows   [128 pairs x k_dim]  K-major, one 16 KB stage per 128-byte K chunk
+//   B = W_k             forward: rows are the contraction index  -> MN-major operand
+//                       dgrad  : rows are the output index (W^T)  -> K-major operand
+//   D = [128 x n_dim] fp32 in TMEM, two buffers
+// =============================================================================================
+template <bool TF32, bool TRANS_W>
+__global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, int n_stage) {
+  using namespace umma;
+  constexpr int ES = TF32 ? 4 : 2;
+  constexpr int EPR = 128 / ES;  // elements per 128-byte span
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align_1024(smem_raw);
+  const uint32_t w_bytes = (uint32_t)p.k_dim * p.n_dim * ES;
+  uint8_t* sW = smem;
+  uint8_t* sStage = smem + w_bytes;
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(sStage + (size_t)n_stage * UMMA_STAGE_BYTES);
+  int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + 256);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int n_seg = p.k_vol + 1;
+  const int kch = p.k_dim / EPR;  // 128-byte K chunks per row
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (tid == 0) {
+    for (int s = 0; s < n_stage; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), UMMA_PROD_THREADS);
+      mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), 128);
+    }
+    sh->abort_flag = 0;
+    mbar_fence_init();
+  }
+  build_tile_table(UMMA_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
+  const uint32_t tmem_cols = tmem_cols_pow2(2u * p.n_dim);
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  int t0, t1;
+  cta_tile_range(tile_start[n_seg], &t0, &t1);
+  bool ok = true;
+
+  if (warp >= 5) {
+    // ------------------------------------------------------------------ producers
+    const int tp = tid - UMMA_PROD_TID0;
+    const int prow = tp >> 3, pc = tp & 7;
+    const uint32_t a_dst0 = (uint32_t)(prow >> 3) * 1024u + (uint32_t)(prow & 7) * 128u + (uint32_t)((pc ^ (prow & 7)) << 4);
+    const uint8_t* src = static_cast<const uint8_t*>(p.src);
+    const uint8_t* wts = static_cast<const uint8_t*>(p.weights);
+    const size_t src_row_bytes = (size_t)p.k_dim * ES;
+    const uint32_t w_row_bytes = (uint32_t)p.c_out * ES;
+    int issued = 0, arrived = 0, cur_w = -1;
+
+    auto flush = [&]() {
+      cp_async_wait<0>();
+      fence_proxy_async();
+      while (arrived < issued) {
+        mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
+        ++arrived;
+      }
+    };
+
+    for (int t = t0; t < t1 && ok; ++t) {
+      const int seg = find_segment(tile_start, n_seg, t);
+      const int lt = t - tile_start[seg];
+      const bool dense = seg == p.k_vol;
+      const int seg_base = dense ? 0 : __ldg(p.kpos + seg);
+      const int seg_cnt = dense ? p.dense_rows : (__ldg(p.kpos + seg + 1) - seg_base);
+      const int cnt = min(UMMA_TILE_M, seg_cnt - lt * UMMA_TILE_M);
+      const int widx = dense ? p.dense_weight : seg;
+
+      int g[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const int row = prow + 16 * i;
+        int v = -1;
+        if (row < cnt) {
+          const int j = lt * UMMA_TILE_M + row;
+          v = dense ? j : __ldg(p.gather_map + seg_base + j);
+          if (v < 0 || v >= p.n_gather) {
+            if (pc == 0) report_problem();
+            v = -1;
+          }
+        }
+        g[i] = v;
+      }
+
+      const bool new_w = widx != cur_w;
+      if (new_w) {
+        // the MMAs of everything issued so far read the old weights: let them finish first
+        flush();
+        if (issued > 0) {
+          const int last = issued - 1;
+          ok = mbar_wait(smem_u32(&sh->empty[last % n_stage]), (uint32_t)(last / n_stage) & 1u, abort_flag);
+          if (!ok) break;
+        }
+        cur_w = widx;
+      }
+
+      for (int kc = 0; kc < kch && ok; ++kc) {
+        const int s = issued % n_stage;
+        ok = mbar_wait(smem_u32(&sh->empty[s]), ((uint32_t)(issued / n_stage) & 1u) ^ 1u, abort_flag);
+        if (!ok) break;
+        if (new_w && kc == 0) {
+          const uint8_t* wk = wts + (size_t)widx * p.c_in * p.c_out * ES;
+          const uint32_t sw = smem_u32(sW);
+          if (!TRANS_W) {
+            // rows = contraction index k (k_dim rows of n_dim elements): MN-major operand
+            const int chunks_per_row = p.n_dim * ES / 16;
+            const int total = p.k_dim * chunks_per_row;
+            const uint32_t lbo = (uint32_t)p.k_dim * 128u;
+            for (int e = tp; e < total; e += UMMA_PROD_THREADS) {
+              const uint32_t row = e / chunks_per_row, c = e % chunks_per_row;
+              const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
+              cp_async16(sw + off, wk + (size_t)row * w_row_bytes + c * 16u, true);
+            }
+          } else {
+            // rows = output index n (n_dim rows of k_dim elements): K-major operand
+            const int chunks_per_row = p.k_dim * ES / 16;
+            const int total = p.n_dim * chunks_per_row;
+            for (int e = tp; e < total; e += UMMA_PROD_THREADS) {
+              const uint32_t row = e / chunks_per_row, c = e % chunks_per_row;
+              cp_async16(sw + kmajor_offset(row, c * 16u, p.n_dim), wk + (size_t)row * w_row_bytes + c * 16u, true);
+            }
+          }
+        }
+        const uint32_t st = smem_u32(sStage + (size_t)s * UMMA_STAGE_BYTES) + a_dst0;
+        const uint8_t* col = src + (size_t)kc * 128 + (size_t)pc * 16;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const bool valid = g[i] >= 0;
+          cp_async16(st + (uint32_t)i * 2048u, valid ? col + (size_t)g[i] * src_row_bytes : src, valid);
+        }
+        cp_async_commit();
+        ++issued;
+        if (issued - arrived > UMMA_LOOKAHEAD) {
+          cp_async_wait<UMMA_LOOKAHEAD>();
+          fence_proxy_async();
+          mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
+          ++arrived;
+        }
+      }
+    }
+    flush();
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = make_idesc(TF32, false, !TRANS_W, UMMA_TILE_M, p.n_dim);
+    const uint32_t sw = smem_u32(sW);
+    int it = 0, tile_i = 0;
+    for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
+      const int buf = tile_i & 1;
+      ok = mbar_wait(smem_u32(&sh->tmem_empty[buf]), ((uint32_t)(tile_i >> 1) & 1u) ^ 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)buf * p.n_dim;
+      for (int kc = 0; kc < kch && ok; ++kc, ++it) {
+        const int s = it % n_stage;
+        ok = mbar_wait(smem_u32(&sh->full[s]), (uint32_t)(it / n_stage) & 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sa = smem_u32(sStage + (size_t)s * UMMA_STAGE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t a_desc = make_sdesc(sa + ks * 32u, 16u, 1024u);
+            uint64_t b_desc;
+            if (!TRANS_W) {
+              // MN-major B: step (kc*EPR + ks*UMMA_K) rows of 128 bytes into the weight tile
+              const uint32_t k_row = (uint32_t)kc * EPR + (uint32_t)ks * (32u / ES);
+              b_desc = make_sdesc(sw + k_row * 128u, (uint32_t)p.k_dim * 128u, TF32 ? 512u : 1024u, TF32 ? 1u : 2u);
+            } else {
+              b_desc = make_sdesc(sw + (uint32_t)kc * ((uint32_t)p.n_dim * 128u) + ks * 32u, 16u, 1024u);
+            }
+            mma_ss<TF32>(d_tmem, a_desc, b_desc, idesc, (kc | ks) != 0);
+          }
+          mma_commit(smem_u32(&sh->empty[s]));
+          if (kc == kch - 1) mma_commit(smem_u32(&sh->tmem_full[buf]));
+        }
+        __syncwarp();
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 0-3)
+    uint8_t* dst = static_cast<uint8_t*>(p.dst);
+    const size_t dst_row_bytes = (size_t)p.n_dim * ES;
+    int tile_i = 0;
+    for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
+      const int seg = find_segment(tile_start, n_seg, t);
+      const int lt = t - tile_start[seg];
+      const bool dense = seg == p.k_vol;
+      const int seg_base = dense ? 0 : __ldg(p.kpos + seg);
+      const int seg_cnt = dense ? p.dense_rows : (__ldg(p.kpos + seg + 1) - seg_base);
+      const int cnt = min(UMMA_TILE_M, seg_cnt - lt * UMMA_TILE_M);
+      int srow = -1;
+      if (tid < cnt) {
+        const int j = lt * UMMA_TILE_M + tid;
+        srow = dense ? j : __ldg(p.scatter_map + seg_base + j);
+        if (srow < 0 || srow >= p.n_scatter) {
+          report_problem();
+          srow = -1;
+        }
+      }
+      const int buf = tile_i & 1;
+      ok = mbar_wait(smem_u32(&sh->tmem_full[buf]), (uint32_t)(tile_i >> 1) & 1u, abort_flag);
+      __syncwarp();
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * p.n_dim;
+      uint8_t* drow = dst + (size_t)(srow < 0 ? 0 : srow) * dst_row_bytes;
+      for (int c0 = 0; c0 < p.n_dim; c0 += 32) {
+        uint32_t v0[16], v1[16];
+        tmem_ld16(taddr + c0, v0);
+        tmem_ld16(taddr + c0 + 16, v1);
+        tmem_ld_wait();
+        if (srow >= 0) {
+          if (TF32) {
+            float* o = reinterpret_cast<float*>(drow) + c0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              red_add_v4(o + 4 * q, __uint_as_float(v0[4 * q]), __uint_as_float(v0[4 * q + 1]),
+                         __uint_as_float(v0[4 * q + 2]), __uint_as_float(v0[4 * q + 3]));
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              red_add_v4(o + 16 + 4 * q, __uint_as_float(v1[4 * q]), __uint_as_float(v1[4 * q + 1]),
+                         __uint_as_float(v1[4 * q + 2]), __uint_as_float(v1[4 * q + 3]));
+          } else {
+            __half* o = reinterpret_cast<__half*>(drow) + c0;
+            uint32_t h[16];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              h[q] = pack_half2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]));
+              h[8 + q] = pack_half2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]));
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q) red_add_h8(o + 8 * q, h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+    }
+  }
+
+  if (!ok && lane == 0) report_problem();
+  cp_async_wait<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// =============================================================================================
+// wgrad:  dw[k] (c_in x c_out, fp32) += sum over the pairs of offset k of feats[in]^T (x) out_grad[out]
+//   the pair index is the contraction index: both operands are gathered rows used MN-major
+//   A = feats rows     [pb pairs x c_in ]   M = c_in  (tiles of 128 rows, or one tile of 64)
+//   B = out_grad rows  [pb pairs x c_out]   N = c_out
+//   The accumulator stays in TMEM while the CTA walks consecutive stages of the same offset and is
+//   flushed with vector red.global.add.f32 when the offset changes (split-K across CTAs).
+// =============================================================================================
+struct WgradTiling {
+  int pb;          // pairs per stage (multiple of 16)
+  int n_mtile;     // 1 or 2 accumulator row tiles
+  int mtile_m;     // rows of each tile's MMA: 128 or 64
+  int alias;       // 1: the single tile has fewer real rows than mtile_m; extra rows repeat (LBO = 0)
+  int n_buf;       // TMEM accumulator sets (2 when they fit)
+  int n_stage;
+};
+
+template <bool TF32>
+__global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams p, WgradTiling tl) {
+  using namespace umma;
+  constexpr int ES = TF32 ? 4 : 2;
+  constexpr int UK = 32 / ES;  // contraction length of one MMA
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = align_1024(smem_raw);
+  const uint32_t a_bytes = (uint32_t)tl.pb * p.c_in * ES;
+  const uint32_t stage_bytes = (uint32_t)tl.pb * (p.c_in + p.c_out) * ES;
+  uint8_t* sStage = smem;
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(sStage + (size_t)tl.n_stage * stage_bytes);
+  int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + 256);
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int n_seg = p.k_vol + 1;
+  const int n_stage = tl.n_stage;
+  volatile int* abort_flag = &sh->abort_flag;
+  const uint32_t lbo = (uint32_t)tl.pb * 128u;  // next 128 bytes of every gathered row
+  const uint32_t buf_cols = (uint32_t)tl.n_mtile * p.c_out;
+
+  if (tid == 0) {
+    for (int s = 0; s < n_stage; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), UMMA_PROD_THREADS);
+      mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), 128);
+    }
+    sh->abort_flag = 0;
+    mbar_fence_init();
+  }
+  build_tile_table(tl.pb, p.kpos, p.k_vol, 0, tile_start);
+  const uint32_t tmem_cols = tmem_cols_pow2(buf_cols * tl.n_buf);
+  if (warp == 4) {
+    tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  int t0, t1;
+  cta_tile_range(tile_start[n_seg], &t0, &t1);
+  bool ok = true;
+
+  if (warp >= 5) {
+    // ------------------------------------------------------------------ producers
+    const int tp = tid - UMMA_PROD_TID0;
+    const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
+    const uint8_t* og = static_cast<const uint8_t*>(p.out_grad);
+    const int ca = p.c_in * ES / 16, cb = p.c_out * ES / 16;  // 16-byte chunks per row
+    const int total_a = tl.pb * ca, total_b = tl.pb * cb;
+    int issued = 0, arrived = 0;
+    for (int t = t0; t < t1 && ok; ++t) {
+      const int seg = find_segment(tile_start, n_seg, t);
+      const int lt = t - tile_start[seg];
+      const int seg_base = __ldg(p.kpos + seg);
+      const int cnt = min(tl.pb, __ldg(p.kpos + seg + 1) - seg_base - lt * tl.pb);
+      const int j0 = seg_base + lt * tl.pb;
+      const int s = issued % n_stage;
+      ok = mbar_wait(smem_u32(&sh->empty[s]), ((uint32_t)(issued / n_stage) & 1u) ^ 1u, abort_flag);
+      if (!ok) break;
+      const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
+      const uint32_t sb = sa + a_bytes;
+      for (int e = tp; e < total_a; e += UMMA_PROD_THREADS) {
+        const uint32_t row = e / ca, c = e % ca;
+        int i = -1;
+        if ((int)row < cnt) {
+          i = __ldg(p.in_map + j0 + row);
+          const int o = __ldg(p.out_map + j0 + row);
+          if (i < 0 || i >= p.n_in || o < 0 || o >= p.n_out) {
+            if (c == 0) report_problem();
+            i = -1;
+          }
+        }
+        const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
+        cp_async16(sa + off, i >= 0 ? feats + ((size_t)i * p.c_in * ES + c * 16u) : feats, i >= 0);
+      }
+      for (int e = tp; e < total_b; e += UMMA_PROD_THREADS) {
+        const uint32_t row = e / cb, c = e % cb;
+        int o = -1;
+        if ((int)row < cnt) {
+          o = __ldg(p.out_map + j0 + row);
+          const int i = __ldg(p.in_map + j0 + row);
+          if (i < 0 || i >= p.n_in || o < 0 || o >= p.n_out) o = -1;
+        }
+        const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
+        cp_async16(sb + off, o >= 0 ? og + ((size_t)o * p.c_out * ES + c * 16u) : og, o >= 0);
+      }
+      cp_async_commit();
+      ++issued;
+      if (issued - arrived > UMMA_LOOKAHEAD) {
+        cp_async_wait<UMMA_LOOKAHEAD>();
+        fence_proxy_async();
+        mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
+        ++arrived;
+      }
+    }
+    cp_async_wait<0>();
+    fence_proxy_async();
+    while (arrived < issued) {
+      mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
+      ++arrived;
+    }
+  } else if (warp == 4) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = make_idesc(TF32, true, true, tl.mtile_m, p.c_out);
+    const uint32_t sbo = TF32 ? 512u : 1024u, ltype = TF32 ? 1u : 2u;
+    const uint32_t a_lbo = tl.alias ? 0u : lbo;
+    const uint32_t mtile_stride = (uint32_t)(tl.mtile_m * ES / 128) * lbo;  // A start of the second row tile
+    int it = 0, run_i = 0, cur_seg = -1;
+    bool first = true;
+    for (int t = t0; t < t1 && ok; ++t, ++it) {
+      const int seg = find_segment(tile_start, n_seg, t);
+      if (seg != cur_seg) {
+        if (cur_seg >= 0) {
+          if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[(run_i % tl.n_buf)]));
+          __syncwarp();
+          ++run_i;
+        }
+        cur_seg = seg;
+        first = true;
+        const int buf = run_i % tl.n_buf;
+        const int use = run_i / tl.n_buf;
+        ok = mbar_wait(smem_u32(&sh->tmem_empty[buf]), ((uint32_t)use & 1u) ^ 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const int buf = run_i % tl.n_buf;
+      const int s = it % n_stage;
+      ok = mbar_wait(smem_u32(&sh->full[s]), (uint32_t)(it / n_stage) & 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
+        const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
+        const uint32_t sb = sa + a_bytes;
+        for (int ks = 0; ks < tl.pb / UK; ++ks) {
+          const uint32_t kadv = (uint32_t)ks * UK * 128u;
+          const uint64_t b_desc = make_sdesc(sb + kadv, lbo, sbo, ltype);
+          for (int mt = 0; mt < tl.n_mtile; ++mt) {
+            const uint64_t a_desc = make_sdesc(sa + kadv + mt * mtile_stride, a_lbo, sbo, ltype);
+            mma_ss<TF32>(tmem_base + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out, a_desc, b_desc, idesc,
+                         !(first && ks == 0));
+          }
+        }
+        mma_commit(smem_u32(&sh->empty[s]));
+      }
+      __syncwarp();
+      first = false;
+    }
+    if (ok && cur_seg >= 0) {
+      if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[(run_i % tl.n_buf)]));
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 0-3)
+    int run_i = 0;
+    int t = t0;
+    while (t < t1 && ok) {
+      const int seg = find_segment(tile_start, n_seg, t);
+      const int seg_end = min(t1, tile_start[seg + 1]);  // this CTA's stages of the offset end here
+      t = seg_end;
+      const int buf = run_i % tl.n_buf;
+      const int use = run_i / tl.n_buf;
+      ok = mbar_wait(smem_u32(&sh->tmem_full[buf]), (uint32_t)use & 1u, abort_flag);
+      __syncwarp();
+      if (!ok) break;
+      tc_fence_after();
+      float* dwk = p.dw + (size_t)seg * p.c_in * p.c_out;
+      for (int mt = 0; mt < tl.n_mtile; ++mt) {
+        // accumulator row held by this thread's TMEM lane
+        int m;
+        if (tl.mtile_m == 128) m = mt * 128 + tid;
+        else m = (lane < 16) ? (warp * 16 + lane) : -1;  // M = 64: row i lives in lane (i/16)*32 + i%16
+        const bool valid = m >= 0 && m < p.c_in;
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out;
+        float* orow = dwk + (size_t)(valid ? m : 0) * p.c_out;
+        for (int c0 = 0; c0 < p.c_out; c0 += 32) {
+          uint32_t v0[16], v1[16];
+          tmem_ld16(taddr + c0, v0);
+          tmem_ld16(taddr + c0 + 16, v1);
+          tmem_ld_wait();
+          if (valid) {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              red_add_v4(orow + c0 + 4 * q, __uint_as_float(v0[4 * q]), __uint_as_float(v0[4 * q + 1]),
+                         __uint_as_float(v0[4 * q + 2]), __uint_as_float(v0[4 * q + 3]));
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              red_add_v4(orow + c0 + 16 + 4 * q, __uint_as_float(v1[4 * q]), __uint_as_float(v1[4 * q + 1]),
+                         __uint_as_float(v1[4 * q + 2]), __uint_as_float(v1[4 * q + 3]));
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+      ++run_i;
+    }
+  }
+
+  if (!ok && lane == 0) report_problem();
+  cp_async_wait<0>();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 4) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// =============================================================================================
+// host launchers: return 0 after a launch, 1 when the shape or the pointers do not fit the
+// tensor-core kernel (the caller then takes the CUDA-core path), < 0 on a CUDA error.
+// =============================================================================================
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename K>
+inline int set_max_smem(K kernel, int bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -1;
+}
+
+inline int launch_umma_gms(const GmsParams& p, bool trans, bool f16, cudaStream_t st, int sms, int max_smem) {
+  const int es = f16 ? 2 : 4;
+  if (!aligned16(p.src) || !aligned16(p.weights) || !aligned16(p.dst)) return 1;
+  const int w_bytes = p.k_dim * p.n_dim * es;
+  const int table = ((p.k_vol + 2) * 4 + 15) & ~15;
+  const int fixed = UMMA_SMEM_FIXED + table;
+  int n_stage = (max_smem - fixed - w_bytes) / UMMA_STAGE_BYTES;
+  if (n_stage > UMMA_MAX_STAGES) n_stage = UMMA_MAX_STAGES;
+  if (n_stage <= UMMA_LOOKAHEAD) return 1;
+  const int smem = fixed + w_bytes + n_stage * UMMA_STAGE_BYTES;
+  int rc;
+  if (f16) {
+    if (trans) { rc = set_max_smem(umma_gms_kernel<false, true>, smem); if (rc) return rc; umma_gms_kernel<false, true><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+    else       { rc = set_max_smem(umma_gms_kernel<false, false>, smem); if (rc) return rc; umma_gms_kernel<false, false><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+  } else {
+    if (trans) { rc = set_max_smem(umma_gms_kernel<true, true>, smem); if (rc) return rc; umma_gms_kernel<true, true><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+    else       { rc = set_max_smem(umma_gms_kernel<true, false>, smem); if (rc) return rc; umma_gms_kernel<true, false><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+  }
+  return 0;
+}
+
+// Accumulator row tiling for c_in: whole 128-row tiles, or a single 64-row tile, or a single tile whose
+// rows beyond c_in repeat the real ones.  Returns false for row counts not covered (e.g. 192).
+inline bool wgrad_tiling(int c_in, int c_out, int es, int max_smem, int k_vol, WgradTiling* tl) {
+  const int span = 128 / es;  // rows per 128-byte span of a gathered feature row
+  if (c_in % 128 == 0) { tl->n_mtile = c_in / 128; tl->mtile_m = 128; tl->alias = 0; }
+  else if (c_in == 64) { tl->n_mtile = 1; tl->mtile_m = 64; tl->alias = 0; }
+  else if (c_in == span) { tl->n_mtile = 1; tl->mtile_m = 64; tl->alias = 1; }  // tf32, 32 rows
+  else return false;
+  if (tl->n_mtile > 2) return false;
+  if (tl->n_mtile * c_out > 512) return false;
+  tl->n_buf = (2 * tl->n_mtile * c_out <= 512) ? 2 : 1;
+  const int row_bytes = (c_in + c_out) * es;
+  int pb = UMMA_STAGE_BYTES / row_bytes;
+  pb = pb / 16 * 16;
+  if (pb < 16) pb = 16;
+  if (pb > 64) pb = 64;
+  tl->pb = pb;
+  const int table = ((k_vol + 2) * 4 + 15) & ~15;
+  int n_stage = (max_smem - UMMA_SMEM_FIXED - table) / (pb * row_bytes);
+  if (n_stage > UMMA_MAX_STAGES) n_stage = UMMA_MAX_STAGES;
+  if (n_stage <= UMMA_LOOKAHEAD) return false;
+  tl->n_stage = n_stage;
+  return true;
+}
+
+inline int launch_umma_wgrad(const WgradParams& p, bool f16, cudaStream_t st, int sms, int max_smem) {
+  const int es = f16 ? 2 : 4;
+  if (!aligned16(p.feats) || !aligned16(p.out_grad) || !aligned16(p.dw)) return 1;
+  WgradTiling tl;
+  if (!wgrad_tiling(p.c_in, p.c_out, es, max_smem, p.k_vol, &tl)) return 1;
+  const int table = ((p.k_vol + 2) * 4 + 15) & ~15;
+  const int smem = UMMA_SMEM_FIXED + table + tl.n_stage * tl.pb * (p.c_in + p.c_out) * es;
+  int rc;
+  if (f16) { rc = set_max_smem(umma_wgrad_kernel<false>, smem); if (rc) return rc; umma_wgrad_kernel<false><<<sms, UMMA_THREADS, smem, st>>>(p, tl); }
+  else     { rc = set_max_smem(umma_wgrad_kernel<true>, smem); if (rc) return rc; umma_wgrad_kernel<true><<<sms, UMMA_THREADS, smem, st>>>(p, tl); }
+  return 0;
+}
+
+}  // namespace fgms
