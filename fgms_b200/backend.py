@@ -23,7 +23,7 @@ import torch
 from . import _lib
 
 __all__ = ["fgms_fusion_fwd_cuda", "fgms_fwd_cuda", "fgms_bwd_cuda", "fgms_dgrad_cuda", "fgms_wgrad_cuda",
-           "wgrad_workspace", "kernel_family", "device_status", "launch_count"]
+           "wgrad_workspace", "wgrad_finalize", "kernel_family", "device_status", "launch_count"]
 
 _L = _lib.lib
 
@@ -189,6 +189,18 @@ def fgms_wgrad_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map, out_map
             _ptr(workspace), workspace.numel() * 4 if workspace is not None else 0, int(bool(accumulate)),
             _stream()))
     return workspace
+
+
+def wgrad_finalize(kernel_grad: torch.Tensor, partial_f32: torch.Tensor) -> None:
+    """``kernel_grad (fp16) += partial_f32`` — the last step of the fp16 weight gradient, exposed so
+    that a multi-GPU caller can all-reduce the fp32 partial sums first."""
+    _check_feat("kernel_grad", kernel_grad, torch.float16, dim=3)
+    if partial_f32.dtype != torch.float32 or not partial_f32.is_cuda or not partial_f32.is_contiguous():
+        raise ValueError("partial sums must be a contiguous CUDA float32 tensor")
+    if partial_f32.numel() < kernel_grad.numel():
+        raise ValueError("partial sums are shorter than kernel_grad")
+    with torch.cuda.device(kernel_grad.device):
+        _lib.check(_L.fgms_b200_wgrad_finalize(_ptr(kernel_grad), _ptr(partial_f32), kernel_grad.numel(), _stream()))
 
 
 def kernel_family(pass_: str, c_in: int, c_out: int, dtype: torch.dtype, arch80: bool = True) -> str:

@@ -1,0 +1,105 @@
+"""Multi-GPU use of the operator: one process per GPU, ``torch.distributed`` for the plumbing.
+
+Two ways the path shards (the reference itself is single-GPU, so this is new):
+
+* **Data parallel over scenes** (``SceneParallelLayer``): every rank holds its own point cloud and a
+  replica of the weights.  Forward and dgrad need no communication.  The weight gradient is the
+  one real exchange step: each rank's fp32 partial ``[k_vol, c_in, c_out]`` is summed with a single
+  all-reduce (NCCL over NVLink on GPUs, gloo on CPU in the tests) and then folded into the
+  caller's ``kernel_grad``.
+* **One scene split over ranks** (``shard_pairs_by_rows``): the pair list of a kernel map is cut by
+  *output-row range* for the forward (each rank owns a contiguous block of output rows, so no two
+  ranks ever accumulate into the same row) and by *input-row range* for dgrad; any disjoint cut
+  serves wgrad, whose partial sums are all-reduced as above.  Range boundaries are placed on the
+  cumulative pair histogram so that ranks get equal pair counts, not equal row counts.
+
+The host-side index work here is NumPy; the per-rank compute is the CUDA operator.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from .maps import KernelMap
+
+__all__ = ["balanced_row_ranges", "shard_pairs_by_rows", "allreduce_sum_", "SceneParallelLayer"]
+
+
+def balanced_row_ranges(rows: np.ndarray, n_rows: int, world: int) -> np.ndarray:
+    """Boundaries ``b[0]=0 <= ... <= b[world]=n_rows`` such that the number of pairs whose row
+    falls in ``[b[r], b[r+1])`` is as equal as a contiguous cut allows."""
+    hist = np.bincount(rows, minlength=n_rows).astype(np.int64) if rows.size else np.zeros(n_rows, np.int64)
+    cum = np.concatenate([[0], np.cumsum(hist)])
+    total = int(cum[-1])
+    bounds = np.zeros(world + 1, dtype=np.int64)
+    bounds[world] = n_rows
+    for r in range(1, world):
+        bounds[r] = int(np.searchsorted(cum, total * r / world, side="left"))
+    return np.maximum.accumulate(np.minimum(bounds, n_rows))
+
+
+def shard_pairs_by_rows(km: KernelMap, world: int, by: str = "out"):
+    """Cut a kernel map into ``world`` kernel maps over the same voxel rows.
+
+    ``by="out"``: rank r gets exactly the pairs whose output row lies in its range (forward);
+    ``by="in"``: the same by input row (dgrad).  Offset-major order and the order inside each
+    offset are kept, and ``kpos`` is re-derived per rank.  Returns ``(shards, bounds)``.
+    """
+    key = km.omap if by == "out" else km.imap
+    n_rows = km.n_out if by == "out" else km.n_in
+    bounds = balanced_row_ranges(key, n_rows, world)
+    seg = np.repeat(np.arange(km.k_vol), km.knnz)
+    owner = np.searchsorted(bounds, key, side="right") - 1
+    owner = np.clip(owner, 0, world - 1)
+    shards = []
+    for r in range(world):
+        sel = owner == r
+        knnz = np.bincount(seg[sel], minlength=km.k_vol).astype(np.int32)
+        kpos = np.zeros(km.k_vol + 1, dtype=np.int32)
+        np.cumsum(knnz, out=kpos[1:])
+        shards.append(KernelMap(km.n_in, km.n_out, km.k_vol, knnz, kpos,
+                                np.ascontiguousarray(km.imap[sel]), np.ascontiguousarray(km.omap[sel]),
+                                km.out_coords))
+    return shards, bounds
+
+
+def allreduce_sum_(tensor, group=None):
+    """In-place sum over all ranks; a no-op outside an initialised process group."""
+    import torch.distributed as dist
+
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(tensor, op=dist.ReduceOp.SUM, group=group)
+    return tensor
+
+
+class SceneParallelLayer:
+    """One sparse-convolution layer trained data-parallel: each rank its own scene.
+
+    ``forward`` / ``backward`` run the CUDA operator on the local scene; ``backward`` sums the fp32
+    weight-gradient partials of all ranks with one all-reduce before adding them to ``w_grad``.
+    """
+
+    def __init__(self, kpos, imap, omap, qsum: int, arch80: bool, group=None):
+        self.kpos, self.imap, self.omap, self.qsum, self.arch80, self.group = kpos, imap, omap, qsum, arch80, group
+
+    def forward(self, feats, weights, out):
+        from . import backend
+        backend.fgms_fusion_fwd_cuda(feats, weights, self.qsum, out, self.kpos, None, self.imap, self.omap,
+                                     False, self.arch80)
+        return out
+
+    def backward(self, grad_out, feats, weights, in_grad, w_grad):
+        import torch
+        from . import backend
+        backend.fgms_dgrad_cuda(grad_out, weights, in_grad, self.kpos, self.imap, self.omap, self.arch80)
+        if feats.dtype == torch.float16:
+            ws = backend.fgms_wgrad_cuda(feats, grad_out, w_grad, self.kpos, self.imap, self.omap, self.arch80,
+                                         accumulate=False)
+            part = ws[: w_grad.numel()]
+            allreduce_sum_(part, self.group)
+            backend.wgrad_finalize(w_grad, part)
+        else:
+            part = torch.zeros_like(w_grad)
+            backend.fgms_wgrad_cuda(feats, grad_out, part, self.kpos, self.imap, self.omap, self.arch80)
+            allreduce_sum_(part, self.group)
+            w_grad += part
+        return in_grad, w_grad

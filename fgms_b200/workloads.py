@@ -20,7 +20,7 @@ from functools import lru_cache
 
 from . import clouds, maps
 
-__all__ = ["Workload", "get", "NAMES", "flops", "algorithmic_bytes"]
+__all__ = ["Workload", "LayerTensors", "get", "NAMES", "flops", "algorithmic_bytes"]
 
 NAMES = ("cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4")
 
@@ -78,3 +78,27 @@ def algorithmic_bytes(wl: Workload, which: str) -> float:
     gms = p * (wl.c_in + wl.c_out) * s + 8 * p + w_elems * s
     wg = p * (wl.c_in + wl.c_out) * s + 8 * p + w_elems * 4
     return {"fwd": gms, "dgrad": gms, "wgrad": wg, "all": 2 * gms + wg}[which]
+
+
+class LayerTensors:
+    """Seeded device tensors of one layer: features, weights, output gradient and the kernel map,
+    laid out as the operator expects them (``mode``: "fp32" | "tf32" | "fp16")."""
+
+    def __init__(self, km: maps.KernelMap, c_in: int, c_out: int, seed: int, mode: str, device="cuda"):
+        import numpy as np
+        import torch
+        self.km, self.c_in, self.c_out, self.mode = km, c_in, c_out, mode
+        npdt = np.float16 if mode == "fp16" else np.float32
+        f, w, g = clouds.make_tensors(km.n_in, km.n_out, c_in, c_out, km.k_vol, seed, npdt)
+        self.f_np, self.w_np, self.g_np = f, w, g
+        dev = torch.device(device)
+        self.feats = torch.from_numpy(f).to(dev)
+        self.weights = torch.from_numpy(w).to(dev)
+        self.grad_out = torch.from_numpy(g).to(dev)
+        self.kpos = torch.from_numpy(km.kpos).to(dev)
+        self.imap = torch.from_numpy(km.imap).to(dev)
+        self.omap = torch.from_numpy(km.omap).to(dev)
+        self.qkpos_np, self.qsum = maps.kpos_quantized(km.knnz, km.kpos, km.k_vol, 256)
+        self.qkpos = torch.from_numpy(self.qkpos_np).to(dev)
+        self.dtype = torch.float16 if mode == "fp16" else torch.float32
+        self.arch80 = mode != "fp32"  # the reference's flag: tensor cores for fp32 storage

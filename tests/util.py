@@ -6,6 +6,7 @@ import numpy as np
 import torch
 
 from fgms_b200 import clouds, maps
+from fgms_b200.workloads import LayerTensors
 from oracle import spconv_oracle as orc
 
 # parity bounds of the task: max-abs error over the tensor, normalised by max |reference|
@@ -20,23 +21,8 @@ def mode_arch80(mode):
     return mode != "fp32"
 
 
-class Problem:
-    def __init__(self, km: maps.KernelMap, c_in: int, c_out: int, seed: int, mode: str, device="cuda"):
-        self.km, self.c_in, self.c_out, self.mode = km, c_in, c_out, mode
-        npdt = np.float16 if mode == "fp16" else np.float32
-        f, w, g = clouds.make_tensors(km.n_in, km.n_out, c_in, c_out, km.k_vol, seed, npdt)
-        self.f_np, self.w_np, self.g_np = f, w, g
-        dev = torch.device(device)
-        self.feats = torch.from_numpy(f).to(dev)
-        self.weights = torch.from_numpy(w).to(dev)
-        self.grad_out = torch.from_numpy(g).to(dev)
-        self.kpos = torch.from_numpy(km.kpos).to(dev)
-        self.imap = torch.from_numpy(km.imap).to(dev)
-        self.omap = torch.from_numpy(km.omap).to(dev)
-        self.qkpos_np, self.qsum = maps.kpos_quantized(km.knnz, km.kpos, km.k_vol, 256)
-        self.qkpos = torch.from_numpy(self.qkpos_np).to(dev)
-        self.dtype = mode_dtype(mode)
-        self.arch80 = mode_arch80(mode)
+class Problem(LayerTensors):
+    """A layer's device tensors plus the oracle answers for them."""
 
     # --- oracle (fp64 on the stored, i.e. already rounded, inputs) ---
     def ref_fwd(self, precompute=False):
