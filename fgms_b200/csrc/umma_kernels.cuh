@@ -7,10 +7,14 @@
 //   warp  4    MMA        one thread issues tcgen05.mma / tcgen05.commit; owns the TMEM allocation
 //   warps 5-8  producers  gather rows with 16-byte cp.async straight into the 128-byte-swizzled
 //                         operand layout tcgen05 reads (no staging copy, no register round trip)
+//   warp  9    index      streams the kernel-map entries of upcoming tiles (coalesced, bounds-checked)
+//                         into a small shared-memory ring, several tiles ahead of everyone else, so
+//                         that no other role ever waits on a dependent global load
 //
-// Shared-memory stages and the two TMEM accumulator buffers are handed between the roles with
-// mbarriers; every wait is bounded (umma::mbar_wait) and a wait that runs out makes all roles leave
-// their loops, reports a problem and still frees the tensor memory.
+// Shared-memory stages, index slots and the TMEM accumulator buffers are handed between the roles
+// with mbarriers (one elected arrival per warp, one polling lane per warp).  Every wait is bounded
+// (umma::mbar_wait): a wait that runs out makes all roles leave their loops, reports a problem and
+// still frees the tensor memory.
 //
 // What these kernels replace in the reference: the wmma forward kernels (backend/fwd_kernels.cuh:17-144,
 // backend/spconv.cuh:1328-1477, 1634-1776), the dgrad kernels (backend/bwd_kernels.cuh:13-142, 281-408)
@@ -25,29 +29,46 @@
 
 namespace fgms {
 
-constexpr int UMMA_THREADS = 288;
+constexpr int UMMA_THREADS = 320;
 constexpr int UMMA_PROD_THREADS = 128;
 constexpr int UMMA_PROD_TID0 = 160;
+constexpr int UMMA_PROD_WARPS = 4;
+constexpr int UMMA_EPI_WARPS = 4;
 constexpr int UMMA_TILE_M = 128;      // pairs per forward / dgrad tile
 constexpr int UMMA_STAGE_BYTES = 16384;
 constexpr int UMMA_MAX_STAGES = 8;
 constexpr int UMMA_LOOKAHEAD = 3;     // cp.async groups a producer thread keeps in flight
-constexpr int UMMA_SMEM_FIXED = 1024 /* alignment slack */ + 512 /* barriers, flags */;
+constexpr int UMMA_IDX_SLOTS = 8;     // index-ring depth (tiles the index warp may run ahead)
+constexpr int UMMA_IDX_BATCH = 4;     // tiles whose map entries the index warp loads at once
+constexpr int UMMA_WG_MAX_PB = 64;    // pairs per wgrad stage, at most
 
 // shapes the tensor-core kernels take: both channel counts fill whole 128-byte spans, at most 256
 inline bool umma_supported(int c_in, int c_out, int elem_bytes) {
   return (c_in * elem_bytes) % 128 == 0 && (c_out * elem_bytes) % 128 == 0 && c_in <= 256 && c_out <= 256;
 }
 
+struct IdxSlot {
+  int seg;     // segment (kernel offset, or k_vol for the dense centre term)
+  int widx;    // weight matrix to use
+  int cnt;     // valid pairs in the tile
+  int pad;
+  int g[UMMA_TILE_M];  // rows to gather  (-1: skip)
+  int s[UMMA_TILE_M];  // rows to scatter (-1: skip)
+};
+
 struct UmmaShared {
   uint64_t full[UMMA_MAX_STAGES];
   uint64_t empty[UMMA_MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
+  uint64_t idx_full[UMMA_IDX_SLOTS];
+  uint64_t idx_empty[UMMA_IDX_SLOTS];
   uint32_t tmem_base;
   int abort_flag;
+  IdxSlot slot[UMMA_IDX_SLOTS];
 };
-static_assert(sizeof(UmmaShared) <= 256, "barrier block must fit its slot");
+constexpr int UMMA_SHARED_BYTES = (sizeof(UmmaShared) + 255) & ~255;
+constexpr int UMMA_SMEM_FIXED = 1024 /* alignment slack */ + UMMA_SHARED_BYTES;
 
 __device__ __forceinline__ uint8_t* align_1024(uint8_t* p) {
   return reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(p) + 1023) & ~static_cast<uintptr_t>(1023));
@@ -57,6 +78,41 @@ __device__ __forceinline__ uint32_t tmem_cols_pow2(uint32_t need) {
   uint32_t c = 32;
   while (c < need) c <<= 1;
   return c;
+}
+
+// one lane polls, the warp learns the outcome
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = umma::mbar_wait(umma::smem_u32(bar), parity, abort_flag) ? 1 : 0;
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+// the warp has finished with something: one arrival for all 32 lanes
+__device__ __forceinline__ void warp_arrive(uint64_t* bar) {
+  __syncwarp();
+  if ((threadIdx.x & 31) == 0) umma::mbar_arrive(umma::smem_u32(bar));
+}
+
+__device__ __forceinline__ void init_barriers(UmmaShared* sh, int n_stage, int idx_consumers) {
+  using namespace umma;
+  for (int s = 0; s < n_stage; ++s) {
+    mbar_init(smem_u32(&sh->full[s]), UMMA_PROD_WARPS);
+    mbar_init(smem_u32(&sh->empty[s]), 1);
+  }
+  for (int b = 0; b < 2; ++b) {
+    mbar_init(smem_u32(&sh->tmem_full[b]), 1);
+    mbar_init(smem_u32(&sh->tmem_empty[b]), UMMA_EPI_WARPS);
+  }
+  for (int i = 0; i < UMMA_IDX_SLOTS; ++i) {
+    mbar_init(smem_u32(&sh->idx_full[i]), 1);
+    mbar_init(smem_u32(&sh->idx_empty[i]), idx_consumers);
+  }
+  sh->abort_flag = 0;
+  mbar_fence_init();
+}
+
+// kpos copied to shared memory next to the tile table, so that tile bookkeeping never leaves the SM
+__device__ __forceinline__ void load_kpos(const int32_t* __restrict__ kpos, int k_vol, int* kpos_s) {
+  for (int s = threadIdx.x; s <= k_vol; s += blockDim.x) kpos_s[s] = __ldg(kpos + s);
 }
 
 // =============================================================================================
@@ -77,7 +133,8 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
   uint8_t* sW = smem;
   uint8_t* sStage = smem + w_bytes;
   UmmaShared* sh = reinterpret_cast<UmmaShared*>(sStage + (size_t)n_stage * UMMA_STAGE_BYTES);
-  int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + 256);
+  int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + UMMA_SHARED_BYTES);  // [k_vol + 2]
+  int* kpos_s = tile_start + p.k_vol + 2;                                                         // [k_vol + 1]
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -85,18 +142,8 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
   const int kch = p.k_dim / EPR;  // 128-byte K chunks per row
   volatile int* abort_flag = &sh->abort_flag;
 
-  if (tid == 0) {
-    for (int s = 0; s < n_stage; ++s) {
-      mbar_init(smem_u32(&sh->full[s]), UMMA_PROD_THREADS);
-      mbar_init(smem_u32(&sh->empty[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
-      mbar_init(smem_u32(&sh->tmem_empty[b]), 128);
-    }
-    sh->abort_flag = 0;
-    mbar_fence_init();
-  }
+  if (tid == 0) init_barriers(sh, n_stage, UMMA_PROD_WARPS + UMMA_EPI_WARPS);
+  load_kpos(p.kpos, p.k_vol, kpos_s);
   build_tile_table(UMMA_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
   const uint32_t tmem_cols = tmem_cols_pow2(2u * p.n_dim);
   if (warp == 4) {
@@ -112,7 +159,67 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
   cta_tile_range(tile_start[n_seg], &t0, &t1);
   bool ok = true;
 
-  if (warp >= 5) {
+  if (warp == 9) {
+    // ------------------------------------------------------------------ index warp
+    for (int tb = t0; tb < t1 && ok; tb += UMMA_IDX_BATCH) {
+      const int nb = min(UMMA_IDX_BATCH, t1 - tb);
+      int g[UMMA_IDX_BATCH][4], s[UMMA_IDX_BATCH][4], seg_[UMMA_IDX_BATCH], cnt_[UMMA_IDX_BATCH];
+#pragma unroll
+      for (int b = 0; b < UMMA_IDX_BATCH; ++b) {
+        if (b < nb) {
+          const int t = tb + b;
+          const int seg = find_segment(tile_start, n_seg, t);
+          const int lt = t - tile_start[seg];
+          const bool dense = seg == p.k_vol;
+          const int seg_base = dense ? 0 : kpos_s[seg];
+          const int seg_cnt = dense ? p.dense_rows : (kpos_s[seg + 1] - seg_base);
+          const int cnt = min(UMMA_TILE_M, seg_cnt - lt * UMMA_TILE_M);
+          seg_[b] = seg;
+          cnt_[b] = cnt;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const int row = lane + 32 * q;
+            const int j = lt * UMMA_TILE_M + row;
+            int gv = -1, sv = -1;
+            if (row < cnt) {
+              gv = dense ? j : __ldg(p.gather_map + seg_base + j);
+              sv = dense ? j : __ldg(p.scatter_map + seg_base + j);
+            }
+            g[b][q] = gv;
+            s[b][q] = sv;
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < UMMA_IDX_BATCH; ++b) {
+        if (b < nb && ok) {
+          const int i = tb + b - t0;
+          const int sl = i % UMMA_IDX_SLOTS;
+          ok = warp_wait(&sh->idx_empty[sl], ((uint32_t)(i / UMMA_IDX_SLOTS) & 1u) ^ 1u, abort_flag);
+          if (ok) {
+            IdxSlot* slot = &sh->slot[sl];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int row = lane + 32 * q;
+              int gv = g[b][q], sv = s[b][q];
+              if (row < cnt_[b] && (gv < 0 || gv >= p.n_gather || sv < 0 || sv >= p.n_scatter)) {
+                report_problem();  // a map entry outside the tensors: the pair is skipped
+                gv = sv = -1;
+              }
+              slot->g[row] = gv;
+              slot->s[row] = sv;
+            }
+            if (lane == 0) {
+              slot->seg = seg_[b];
+              slot->widx = seg_[b] == p.k_vol ? p.dense_weight : seg_[b];
+              slot->cnt = cnt_[b];
+            }
+            warp_arrive(&sh->idx_full[sl]);
+          }
+        }
+      }
+    }
+  } else if (warp >= 5) {
     // ------------------------------------------------------------------ producers
     const int tp = tid - UMMA_PROD_TID0;
     const int prow = tp >> 3, pc = tp & 7;
@@ -126,36 +233,24 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
     auto flush = [&]() {
       cp_async_wait<0>();
       fence_proxy_async();
+      __syncwarp();
       while (arrived < issued) {
-        mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
+        if (lane == 0) mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
         ++arrived;
       }
     };
 
     for (int t = t0; t < t1 && ok; ++t) {
-      const int seg = find_segment(tile_start, n_seg, t);
-      const int lt = t - tile_start[seg];
-      const bool dense = seg == p.k_vol;
-      const int seg_base = dense ? 0 : __ldg(p.kpos + seg);
-      const int seg_cnt = dense ? p.dense_rows : (__ldg(p.kpos + seg + 1) - seg_base);
-      const int cnt = min(UMMA_TILE_M, seg_cnt - lt * UMMA_TILE_M);
-      const int widx = dense ? p.dense_weight : seg;
-
+      const int i = t - t0;
+      const int sl = i % UMMA_IDX_SLOTS;
+      ok = warp_wait(&sh->idx_full[sl], (uint32_t)(i / UMMA_IDX_SLOTS) & 1u, abort_flag);
+      if (!ok) break;
+      const IdxSlot* slot = &sh->slot[sl];
+      const int widx = slot->widx;
       int g[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int row = prow + 16 * i;
-        int v = -1;
-        if (row < cnt) {
-          const int j = lt * UMMA_TILE_M + row;
-          v = dense ? j : __ldg(p.gather_map + seg_base + j);
-          if (v < 0 || v >= p.n_gather) {
-            if (pc == 0) report_problem();
-            v = -1;
-          }
-        }
-        g[i] = v;
-      }
+      for (int q = 0; q < 8; ++q) g[q] = slot->g[prow + 16 * q];
+      warp_arrive(&sh->idx_empty[sl]);
 
       const bool new_w = widx != cur_w;
       if (new_w) {
@@ -163,7 +258,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
         flush();
         if (issued > 0) {
           const int last = issued - 1;
-          ok = mbar_wait(smem_u32(&sh->empty[last % n_stage]), (uint32_t)(last / n_stage) & 1u, abort_flag);
+          ok = warp_wait(&sh->empty[last % n_stage], (uint32_t)(last / n_stage) & 1u, abort_flag);
           if (!ok) break;
         }
         cur_w = widx;
@@ -171,7 +266,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
 
       for (int kc = 0; kc < kch && ok; ++kc) {
         const int s = issued % n_stage;
-        ok = mbar_wait(smem_u32(&sh->empty[s]), ((uint32_t)(issued / n_stage) & 1u) ^ 1u, abort_flag);
+        ok = warp_wait(&sh->empty[s], ((uint32_t)(issued / n_stage) & 1u) ^ 1u, abort_flag);
         if (!ok) break;
         if (new_w && kc == 0) {
           const uint8_t* wk = wts + (size_t)widx * p.c_in * p.c_out * ES;
@@ -199,16 +294,16 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
         const uint32_t st = smem_u32(sStage + (size_t)s * UMMA_STAGE_BYTES) + a_dst0;
         const uint8_t* col = src + (size_t)kc * 128 + (size_t)pc * 16;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const bool valid = g[i] >= 0;
-          cp_async16(st + (uint32_t)i * 2048u, valid ? col + (size_t)g[i] * src_row_bytes : src, valid);
+        for (int q = 0; q < 8; ++q) {
+          const bool valid = g[q] >= 0;
+          cp_async16(st + (uint32_t)q * 2048u, valid ? col + (size_t)g[q] * src_row_bytes : src, valid);
         }
         cp_async_commit();
         ++issued;
         if (issued - arrived > UMMA_LOOKAHEAD) {
           cp_async_wait<UMMA_LOOKAHEAD>();
           fence_proxy_async();
-          mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
+          warp_arrive(&sh->full[arrived % n_stage]);
           ++arrived;
         }
       }
@@ -221,13 +316,13 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
     int it = 0, tile_i = 0;
     for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
       const int buf = tile_i & 1;
-      ok = mbar_wait(smem_u32(&sh->tmem_empty[buf]), ((uint32_t)(tile_i >> 1) & 1u) ^ 1u, abort_flag);
+      ok = warp_wait(&sh->tmem_empty[buf], ((uint32_t)(tile_i >> 1) & 1u) ^ 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)buf * p.n_dim;
       for (int kc = 0; kc < kch && ok; ++kc, ++it) {
         const int s = it % n_stage;
-        ok = mbar_wait(smem_u32(&sh->full[s]), (uint32_t)(it / n_stage) & 1u, abort_flag);
+        ok = warp_wait(&sh->full[s], (uint32_t)(it / n_stage) & 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
@@ -257,59 +352,56 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
     const size_t dst_row_bytes = (size_t)p.n_dim * ES;
     int tile_i = 0;
     for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
-      const int seg = find_segment(tile_start, n_seg, t);
-      const int lt = t - tile_start[seg];
-      const bool dense = seg == p.k_vol;
-      const int seg_base = dense ? 0 : __ldg(p.kpos + seg);
-      const int seg_cnt = dense ? p.dense_rows : (__ldg(p.kpos + seg + 1) - seg_base);
-      const int cnt = min(UMMA_TILE_M, seg_cnt - lt * UMMA_TILE_M);
-      int srow = -1;
-      if (tid < cnt) {
-        const int j = lt * UMMA_TILE_M + tid;
-        srow = dense ? j : __ldg(p.scatter_map + seg_base + j);
-        if (srow < 0 || srow >= p.n_scatter) {
-          report_problem();
-          srow = -1;
-        }
-      }
+      const int sl = tile_i % UMMA_IDX_SLOTS;
+      ok = warp_wait(&sh->idx_full[sl], (uint32_t)(tile_i / UMMA_IDX_SLOTS) & 1u, abort_flag);
+      if (!ok) break;
+      const int srow = sh->slot[sl].s[tid];
+      warp_arrive(&sh->idx_empty[sl]);
+
       const int buf = tile_i & 1;
-      ok = mbar_wait(smem_u32(&sh->tmem_full[buf]), (uint32_t)(tile_i >> 1) & 1u, abort_flag);
-      __syncwarp();
+      ok = warp_wait(&sh->tmem_full[buf], (uint32_t)(tile_i >> 1) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * p.n_dim;
       uint8_t* drow = dst + (size_t)(srow < 0 ? 0 : srow) * dst_row_bytes;
-      for (int c0 = 0; c0 < p.n_dim; c0 += 32) {
-        uint32_t v0[16], v1[16];
-        tmem_ld16(taddr + c0, v0);
-        tmem_ld16(taddr + c0 + 16, v1);
+      for (int c0 = 0; c0 < p.n_dim; c0 += 64) {
+        // 64 columns at a time (n_dim is a multiple of 32)
+        const bool second = c0 + 32 < p.n_dim;
+        uint32_t v[4][16];
+        tmem_ld16(taddr + c0, v[0]);
+        tmem_ld16(taddr + c0 + 16, v[1]);
+        if (second) {
+          tmem_ld16(taddr + c0 + 32, v[2]);
+          tmem_ld16(taddr + c0 + 48, v[3]);
+        }
         tmem_ld_wait();
+        if (c0 + 64 >= p.n_dim) {
+          // accumulator fully read: hand the TMEM buffer back before the (slower) scatter
+          tc_fence_before();
+          warp_arrive(&sh->tmem_empty[buf]);
+        }
         if (srow >= 0) {
-          if (TF32) {
-            float* o = reinterpret_cast<float*>(drow) + c0;
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-              red_add_v4(o + 4 * q, __uint_as_float(v0[4 * q]), __uint_as_float(v0[4 * q + 1]),
-                         __uint_as_float(v0[4 * q + 2]), __uint_as_float(v0[4 * q + 3]));
+          for (int h = 0; h < 4; ++h) {
+            if (h < 2 || second) {
+              if (TF32) {
+                float* o = reinterpret_cast<float*>(drow) + c0 + 16 * h;
 #pragma unroll
-            for (int q = 0; q < 4; ++q)
-              red_add_v4(o + 16 + 4 * q, __uint_as_float(v1[4 * q]), __uint_as_float(v1[4 * q + 1]),
-                         __uint_as_float(v1[4 * q + 2]), __uint_as_float(v1[4 * q + 3]));
-          } else {
-            __half* o = reinterpret_cast<__half*>(drow) + c0;
-            uint32_t h[16];
+                for (int q = 0; q < 4; ++q)
+                  red_add_v4(o + 4 * q, __uint_as_float(v[h][4 * q]), __uint_as_float(v[h][4 * q + 1]),
+                             __uint_as_float(v[h][4 * q + 2]), __uint_as_float(v[h][4 * q + 3]));
+              } else {
+                __half* o = reinterpret_cast<__half*>(drow) + c0 + 16 * h;
+                uint32_t hh[8];
 #pragma unroll
-            for (int q = 0; q < 8; ++q) {
-              h[q] = pack_half2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]));
-              h[8 + q] = pack_half2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]));
+                for (int q = 0; q < 8; ++q) hh[q] = pack_half2(__uint_as_float(v[h][2 * q]), __uint_as_float(v[h][2 * q + 1]));
+                red_add_h8(o, hh[0], hh[1], hh[2], hh[3]);
+                red_add_h8(o + 8, hh[4], hh[5], hh[6], hh[7]);
+              }
             }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) red_add_h8(o + 8 * q, h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
           }
         }
       }
-      tc_fence_before();
-      mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
     }
   }
 
@@ -329,7 +421,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
 //   flushed with vector red.global.add.f32 when the offset changes (split-K across CTAs).
 // =============================================================================================
 struct WgradTiling {
-  int pb;          // pairs per stage (multiple of 16)
+  int pb;          // pairs per stage (multiple of 16, at most UMMA_WG_MAX_PB)
   int n_mtile;     // 1 or 2 accumulator row tiles
   int mtile_m;     // rows of each tile's MMA: 128 or 64
   int alias;       // 1: the single tile has fewer real rows than mtile_m; extra rows repeat (LBO = 0)
@@ -348,7 +440,8 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
   const uint32_t stage_bytes = (uint32_t)tl.pb * (p.c_in + p.c_out) * ES;
   uint8_t* sStage = smem;
   UmmaShared* sh = reinterpret_cast<UmmaShared*>(sStage + (size_t)tl.n_stage * stage_bytes);
-  int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + 256);
+  int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + UMMA_SHARED_BYTES);
+  int* kpos_s = tile_start + p.k_vol + 2;
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -358,18 +451,8 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
   const uint32_t lbo = (uint32_t)tl.pb * 128u;  // next 128 bytes of every gathered row
   const uint32_t buf_cols = (uint32_t)tl.n_mtile * p.c_out;
 
-  if (tid == 0) {
-    for (int s = 0; s < n_stage; ++s) {
-      mbar_init(smem_u32(&sh->full[s]), UMMA_PROD_THREADS);
-      mbar_init(smem_u32(&sh->empty[s]), 1);
-    }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
-      mbar_init(smem_u32(&sh->tmem_empty[b]), 128);
-    }
-    sh->abort_flag = 0;
-    mbar_fence_init();
-  }
+  if (tid == 0) init_barriers(sh, n_stage, UMMA_PROD_WARPS + 1);
+  load_kpos(p.kpos, p.k_vol, kpos_s);
   build_tile_table(tl.pb, p.kpos, p.k_vol, 0, tile_start);
   const uint32_t tmem_cols = tmem_cols_pow2(buf_cols * tl.n_buf);
   if (warp == 4) {
@@ -385,63 +468,109 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
   cta_tile_range(tile_start[n_seg], &t0, &t1);
   bool ok = true;
 
-  if (warp >= 5) {
+  if (warp == 9) {
+    // ------------------------------------------------------------------ index warp (pb <= 64 pairs per stage)
+    for (int tb = t0; tb < t1 && ok; tb += UMMA_IDX_BATCH) {
+      const int nb = min(UMMA_IDX_BATCH, t1 - tb);
+      int iv[UMMA_IDX_BATCH][2], ov[UMMA_IDX_BATCH][2], seg_[UMMA_IDX_BATCH], cnt_[UMMA_IDX_BATCH];
+#pragma unroll
+      for (int b = 0; b < UMMA_IDX_BATCH; ++b) {
+        if (b < nb) {
+          const int t = tb + b;
+          const int seg = find_segment(tile_start, n_seg, t);
+          const int lt = t - tile_start[seg];
+          const int seg_base = kpos_s[seg];
+          const int cnt = min(tl.pb, kpos_s[seg + 1] - seg_base - lt * tl.pb);
+          seg_[b] = seg;
+          cnt_[b] = cnt;
+#pragma unroll
+          for (int q = 0; q < 2; ++q) {
+            const int row = lane + 32 * q;
+            int a = -1, o = -1;
+            if (row < cnt) {
+              a = __ldg(p.in_map + seg_base + lt * tl.pb + row);
+              o = __ldg(p.out_map + seg_base + lt * tl.pb + row);
+            }
+            iv[b][q] = a;
+            ov[b][q] = o;
+          }
+        }
+      }
+#pragma unroll
+      for (int b = 0; b < UMMA_IDX_BATCH; ++b) {
+        if (b < nb && ok) {
+          const int i = tb + b - t0;
+          const int sl = i % UMMA_IDX_SLOTS;
+          ok = warp_wait(&sh->idx_empty[sl], ((uint32_t)(i / UMMA_IDX_SLOTS) & 1u) ^ 1u, abort_flag);
+          if (ok) {
+            IdxSlot* slot = &sh->slot[sl];
+#pragma unroll
+            for (int q = 0; q < 2; ++q) {
+              const int row = lane + 32 * q;
+              int a = iv[b][q], o = ov[b][q];
+              if (row < cnt_[b] && (a < 0 || a >= p.n_in || o < 0 || o >= p.n_out)) {
+                report_problem();
+                a = o = -1;
+              }
+              slot->g[row] = a;
+              slot->s[row] = o;
+            }
+            if (lane == 0) {
+              slot->seg = seg_[b];
+              slot->cnt = cnt_[b];
+            }
+            warp_arrive(&sh->idx_full[sl]);
+          }
+        }
+      }
+    }
+  } else if (warp >= 5) {
     // ------------------------------------------------------------------ producers
     const int tp = tid - UMMA_PROD_TID0;
     const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
     const uint8_t* og = static_cast<const uint8_t*>(p.out_grad);
     const int ca = p.c_in * ES / 16, cb = p.c_out * ES / 16;  // 16-byte chunks per row
     const int total_a = tl.pb * ca, total_b = tl.pb * cb;
+    const size_t a_row_bytes = (size_t)p.c_in * ES, b_row_bytes = (size_t)p.c_out * ES;
     int issued = 0, arrived = 0;
     for (int t = t0; t < t1 && ok; ++t) {
-      const int seg = find_segment(tile_start, n_seg, t);
-      const int lt = t - tile_start[seg];
-      const int seg_base = __ldg(p.kpos + seg);
-      const int cnt = min(tl.pb, __ldg(p.kpos + seg + 1) - seg_base - lt * tl.pb);
-      const int j0 = seg_base + lt * tl.pb;
+      const int i = t - t0;
+      const int sl = i % UMMA_IDX_SLOTS;
+      ok = warp_wait(&sh->idx_full[sl], (uint32_t)(i / UMMA_IDX_SLOTS) & 1u, abort_flag);
+      if (!ok) break;
+      const IdxSlot* slot = &sh->slot[sl];
       const int s = issued % n_stage;
-      ok = mbar_wait(smem_u32(&sh->empty[s]), ((uint32_t)(issued / n_stage) & 1u) ^ 1u, abort_flag);
+      ok = warp_wait(&sh->empty[s], ((uint32_t)(issued / n_stage) & 1u) ^ 1u, abort_flag);
       if (!ok) break;
       const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
       const uint32_t sb = sa + a_bytes;
       for (int e = tp; e < total_a; e += UMMA_PROD_THREADS) {
         const uint32_t row = e / ca, c = e % ca;
-        int i = -1;
-        if ((int)row < cnt) {
-          i = __ldg(p.in_map + j0 + row);
-          const int o = __ldg(p.out_map + j0 + row);
-          if (i < 0 || i >= p.n_in || o < 0 || o >= p.n_out) {
-            if (c == 0) report_problem();
-            i = -1;
-          }
-        }
+        const int a = slot->g[row];
         const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
-        cp_async16(sa + off, i >= 0 ? feats + ((size_t)i * p.c_in * ES + c * 16u) : feats, i >= 0);
+        cp_async16(sa + off, a >= 0 ? feats + ((size_t)a * a_row_bytes + c * 16u) : feats, a >= 0);
       }
       for (int e = tp; e < total_b; e += UMMA_PROD_THREADS) {
         const uint32_t row = e / cb, c = e % cb;
-        int o = -1;
-        if ((int)row < cnt) {
-          o = __ldg(p.out_map + j0 + row);
-          const int i = __ldg(p.in_map + j0 + row);
-          if (i < 0 || i >= p.n_in || o < 0 || o >= p.n_out) o = -1;
-        }
+        const int o = slot->s[row];
         const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
-        cp_async16(sb + off, o >= 0 ? og + ((size_t)o * p.c_out * ES + c * 16u) : og, o >= 0);
+        cp_async16(sb + off, o >= 0 ? og + ((size_t)o * b_row_bytes + c * 16u) : og, o >= 0);
       }
       cp_async_commit();
+      warp_arrive(&sh->idx_empty[sl]);
       ++issued;
       if (issued - arrived > UMMA_LOOKAHEAD) {
         cp_async_wait<UMMA_LOOKAHEAD>();
         fence_proxy_async();
-        mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
+        warp_arrive(&sh->full[arrived % n_stage]);
         ++arrived;
       }
     }
     cp_async_wait<0>();
     fence_proxy_async();
+    __syncwarp();
     while (arrived < issued) {
-      mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
+      if (lane == 0) mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
       ++arrived;
     }
   } else if (warp == 4) {
@@ -453,7 +582,11 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
     int it = 0, run_i = 0, cur_seg = -1;
     bool first = true;
     for (int t = t0; t < t1 && ok; ++t, ++it) {
-      const int seg = find_segment(tile_start, n_seg, t);
+      const int sl = it % UMMA_IDX_SLOTS;
+      ok = warp_wait(&sh->idx_full[sl], (uint32_t)(it / UMMA_IDX_SLOTS) & 1u, abort_flag);
+      if (!ok) break;
+      const int seg = sh->slot[sl].seg;
+      warp_arrive(&sh->idx_empty[sl]);
       if (seg != cur_seg) {
         if (cur_seg >= 0) {
           if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[(run_i % tl.n_buf)]));
@@ -464,13 +597,13 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
         first = true;
         const int buf = run_i % tl.n_buf;
         const int use = run_i / tl.n_buf;
-        ok = mbar_wait(smem_u32(&sh->tmem_empty[buf]), ((uint32_t)use & 1u) ^ 1u, abort_flag);
+        ok = warp_wait(&sh->tmem_empty[buf], ((uint32_t)use & 1u) ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
       }
       const int buf = run_i % tl.n_buf;
       const int s = it % n_stage;
-      ok = mbar_wait(smem_u32(&sh->full[s]), (uint32_t)(it / n_stage) & 1u, abort_flag);
+      ok = warp_wait(&sh->full[s], (uint32_t)(it / n_stage) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
       if (lane == 0) {
@@ -504,8 +637,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
       t = seg_end;
       const int buf = run_i % tl.n_buf;
       const int use = run_i / tl.n_buf;
-      ok = mbar_wait(smem_u32(&sh->tmem_full[buf]), (uint32_t)use & 1u, abort_flag);
-      __syncwarp();
+      ok = warp_wait(&sh->tmem_full[buf], (uint32_t)use & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
       float* dwk = p.dw + (size_t)seg * p.c_in * p.c_out;
@@ -535,7 +667,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+      warp_arrive(&sh->tmem_empty[buf]);
       ++run_i;
     }
   }
@@ -553,28 +685,37 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
 // =============================================================================================
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+inline int umma_table_bytes(int k_vol) { return ((2 * k_vol + 3) * 4 + 15) & ~15; }
+
+// cudaFuncSetAttribute is needed once per device and kernel; remember what was granted
 template <typename K>
-inline int set_max_smem(K kernel, int bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) == cudaSuccess ? 0 : -1;
+inline int ensure_smem(K kernel, int bytes, int slot) {
+  static int granted[8][64] = {};  // [kernel slot][device]
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return -1;
+  if (dev < 0 || dev >= 64) return -1;
+  if (granted[slot][dev] >= bytes) return 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -1;
+  granted[slot][dev] = bytes;
+  return 0;
 }
 
 inline int launch_umma_gms(const GmsParams& p, bool trans, bool f16, cudaStream_t st, int sms, int max_smem) {
   const int es = f16 ? 2 : 4;
   if (!aligned16(p.src) || !aligned16(p.weights) || !aligned16(p.dst)) return 1;
   const int w_bytes = p.k_dim * p.n_dim * es;
-  const int table = ((p.k_vol + 2) * 4 + 15) & ~15;
-  const int fixed = UMMA_SMEM_FIXED + table;
+  const int fixed = UMMA_SMEM_FIXED + umma_table_bytes(p.k_vol);
   int n_stage = (max_smem - fixed - w_bytes) / UMMA_STAGE_BYTES;
   if (n_stage > UMMA_MAX_STAGES) n_stage = UMMA_MAX_STAGES;
   if (n_stage <= UMMA_LOOKAHEAD) return 1;
   const int smem = fixed + w_bytes + n_stage * UMMA_STAGE_BYTES;
   int rc;
   if (f16) {
-    if (trans) { rc = set_max_smem(umma_gms_kernel<false, true>, smem); if (rc) return rc; umma_gms_kernel<false, true><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
-    else       { rc = set_max_smem(umma_gms_kernel<false, false>, smem); if (rc) return rc; umma_gms_kernel<false, false><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+    if (trans) { rc = ensure_smem(umma_gms_kernel<false, true>, max_smem, 0); if (rc) return rc; umma_gms_kernel<false, true><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+    else       { rc = ensure_smem(umma_gms_kernel<false, false>, max_smem, 1); if (rc) return rc; umma_gms_kernel<false, false><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
   } else {
-    if (trans) { rc = set_max_smem(umma_gms_kernel<true, true>, smem); if (rc) return rc; umma_gms_kernel<true, true><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
-    else       { rc = set_max_smem(umma_gms_kernel<true, false>, smem); if (rc) return rc; umma_gms_kernel<true, false><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+    if (trans) { rc = ensure_smem(umma_gms_kernel<true, true>, max_smem, 2); if (rc) return rc; umma_gms_kernel<true, true><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+    else       { rc = ensure_smem(umma_gms_kernel<true, false>, max_smem, 3); if (rc) return rc; umma_gms_kernel<true, false><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
   }
   return 0;
 }
@@ -594,10 +735,9 @@ inline bool wgrad_tiling(int c_in, int c_out, int es, int max_smem, int k_vol, W
   int pb = UMMA_STAGE_BYTES / row_bytes;
   pb = pb / 16 * 16;
   if (pb < 16) pb = 16;
-  if (pb > 64) pb = 64;
+  if (pb > UMMA_WG_MAX_PB) pb = UMMA_WG_MAX_PB;
   tl->pb = pb;
-  const int table = ((k_vol + 2) * 4 + 15) & ~15;
-  int n_stage = (max_smem - UMMA_SMEM_FIXED - table) / (pb * row_bytes);
+  int n_stage = (max_smem - UMMA_SMEM_FIXED - umma_table_bytes(k_vol)) / (pb * row_bytes);
   if (n_stage > UMMA_MAX_STAGES) n_stage = UMMA_MAX_STAGES;
   if (n_stage <= UMMA_LOOKAHEAD) return false;
   tl->n_stage = n_stage;
@@ -609,11 +749,10 @@ inline int launch_umma_wgrad(const WgradParams& p, bool f16, cudaStream_t st, in
   if (!aligned16(p.feats) || !aligned16(p.out_grad) || !aligned16(p.dw)) return 1;
   WgradTiling tl;
   if (!wgrad_tiling(p.c_in, p.c_out, es, max_smem, p.k_vol, &tl)) return 1;
-  const int table = ((p.k_vol + 2) * 4 + 15) & ~15;
-  const int smem = UMMA_SMEM_FIXED + table + tl.n_stage * tl.pb * (p.c_in + p.c_out) * es;
+  const int smem = UMMA_SMEM_FIXED + umma_table_bytes(p.k_vol) + tl.n_stage * tl.pb * (p.c_in + p.c_out) * es;
   int rc;
-  if (f16) { rc = set_max_smem(umma_wgrad_kernel<false>, smem); if (rc) return rc; umma_wgrad_kernel<false><<<sms, UMMA_THREADS, smem, st>>>(p, tl); }
-  else     { rc = set_max_smem(umma_wgrad_kernel<true>, smem); if (rc) return rc; umma_wgrad_kernel<true><<<sms, UMMA_THREADS, smem, st>>>(p, tl); }
+  if (f16) { rc = ensure_smem(umma_wgrad_kernel<false>, max_smem, 4); if (rc) return rc; umma_wgrad_kernel<false><<<sms, UMMA_THREADS, smem, st>>>(p, tl); }
+  else     { rc = ensure_smem(umma_wgrad_kernel<true>, max_smem, 5); if (rc) return rc; umma_wgrad_kernel<true><<<sms, UMMA_THREADS, smem, st>>>(p, tl); }
   return 0;
 }
 
