@@ -25,11 +25,14 @@ __device__ __forceinline__ void mbar_fence_init() {
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// One non-blocking probe of the barrier.  (mbarrier.try_wait may park the thread for an
+// implementation-defined time slice and was measured to wake up late; hand-offs between the roles of
+// these kernels are latency-critical, so the waiting lane probes with test_wait instead.)
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
       : "r"(bar), "r"(parity)
@@ -44,10 +47,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   const long long start = clock64();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 31) == 0) {
+    if ((it & 255u) == 0) {
       if (abort_flag && *abort_flag) return false;
       if (clock64() - start > WAIT_LIMIT_CYCLES) break;
-      __nanosleep(32);
     }
   }
   if (abort_flag) *abort_flag = 1;
@@ -64,8 +66,41 @@ template <int N>
 __device__ __forceinline__ void cp_async_wait() {
   asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+// the mbarrier receives one arrival from this thread once all cp.async it has issued so far have landed
+// (.noinc: the arrival counts against the barrier's expected count like an ordinary arrive)
+__device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
+}
 // make generic-proxy / cp.async writes to shared memory visible to the async proxy (tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// ------------------------------------------------------------------ bulk (TMA engine) reduction smem -> global
+// dst[0..bytes) += src[0..bytes) element-wise, performed asynchronously by the copy engine.  Both
+// addresses 16-byte aligned, bytes a multiple of 16.  The calling thread tracks completion with its
+// own bulk groups.
+template <bool F32>
+__device__ __forceinline__ void bulk_reduce_add(void* dst_global, uint32_t src_smem, uint32_t bytes) {
+  if (F32) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst_global),
+                 "r"(src_smem), "r"(bytes)
+                 : "memory");
+  } else {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;" ::"l"(dst_global),
+                 "r"(src_smem), "r"(bytes)
+                 : "memory");
+  }
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// wait until at most N of this thread's bulk groups still have to READ their shared-memory source
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 
 // ------------------------------------------------------------------ tcgen05
 __device__ __forceinline__ bool elect_one() {

@@ -3,13 +3,18 @@
 // Both kernels are persistent (one CTA per SM, each walking a contiguous share of the tile list
 // derived from `kpos`) and warp-specialised:
 //
-//   warps 0-3  epilogue   tcgen05.ld of the fp32 accumulators, conversion, vector red.global.add
+//   warps 0-3  drain      tcgen05.ld of the fp32 accumulators, conversion to the storage type, parked in a
+//                         swizzled shared-memory patch (wgrad: straight to vector red.global.add.f32)
 //   warp  4    MMA        one thread issues tcgen05.mma / tcgen05.commit; owns the TMEM allocation
 //   warps 5-8  producers  gather rows with 16-byte cp.async straight into the 128-byte-swizzled
 //                         operand layout tcgen05 reads (no staging copy, no register round trip)
 //   warp  9    index      streams the kernel-map entries of upcoming tiles (coalesced, bounds-checked)
 //                         into a small shared-memory ring, several tiles ahead of everyone else, so
 //                         that no other role ever waits on a dependent global load
+//   warps 10-13 scatter   (forward / dgrad) read the patch back so that 8 or 16 consecutive lanes cover one
+//                         destination row and issue vector red.global.add.  The SM's reduction path tops
+//                         out near 25 bytes per cycle (measured); four warps that alternate between
+//                         reading the patch and issuing reds get within about 20 % of it
 //
 // Shared-memory stages, index slots and the TMEM accumulator buffers are handed between the roles
 // with mbarriers (one elected arrival per warp, one polling lane per warp).  Every wait is bounded
@@ -29,7 +34,9 @@
 
 namespace fgms {
 
-constexpr int UMMA_THREADS = 320;
+constexpr int UMMA_THREADS = 320;       // wgrad: warps 0-9
+constexpr int UMMA_GMS_THREADS = 448;   // forward / dgrad: four more warps for the scatter
+constexpr int UMMA_SCATTER_WARPS = 4;
 constexpr int UMMA_PROD_THREADS = 128;
 constexpr int UMMA_PROD_TID0 = 160;
 constexpr int UMMA_PROD_WARPS = 4;
@@ -37,23 +44,29 @@ constexpr int UMMA_EPI_WARPS = 4;
 constexpr int UMMA_TILE_M = 128;      // pairs per forward / dgrad tile
 constexpr int UMMA_STAGE_BYTES = 16384;
 constexpr int UMMA_MAX_STAGES = 8;
-constexpr int UMMA_LOOKAHEAD = 3;     // cp.async groups a producer thread keeps in flight
-constexpr int UMMA_IDX_SLOTS = 8;     // index-ring depth (tiles the index warp may run ahead)
-constexpr int UMMA_IDX_BATCH = 4;     // tiles whose map entries the index warp loads at once
+constexpr int UMMA_IDX_SLOTS = 16;    // index-ring depth (tiles the index warp may run ahead)
+constexpr int UMMA_IDX_BATCH = 8;     // tiles whose map entries the index warp loads at once
 constexpr int UMMA_WG_MAX_PB = 64;    // pairs per wgrad stage, at most
+constexpr int UMMA_PATCH_BYTES = UMMA_TILE_M * 256;  // one 256-byte block of every row of a tile
+constexpr int UMMA_MAX_PATCHES = 2;  // patches are filled and scattered alternately when two fit
 
 // shapes the tensor-core kernels take: both channel counts fill whole 128-byte spans, at most 256
 inline bool umma_supported(int c_in, int c_out, int elem_bytes) {
   return (c_in * elem_bytes) % 128 == 0 && (c_out * elem_bytes) % 128 == 0 && c_in <= 256 && c_out <= 256;
 }
 
-struct IdxSlot {
+// What the index warp publishes per tile.  Gather side (read by the producers; the MMA warp reads
+// `seg` in wgrad) and scatter side (read by the epilogue) live in separate rings so that the slow
+// consumer of one never holds back the other.
+struct GatherSlot {
   int seg;     // segment (kernel offset, or k_vol for the dense centre term)
   int widx;    // weight matrix to use
   int cnt;     // valid pairs in the tile
   int pad;
-  int g[UMMA_TILE_M];  // rows to gather  (-1: skip)
-  int s[UMMA_TILE_M];  // rows to scatter (-1: skip)
+  int g[UMMA_TILE_M];  // rows to gather (-1: skip).  wgrad: [0,64) input rows, [64,128) output rows
+};
+struct ScatterSlot {
+  int s[UMMA_TILE_M];  // rows to accumulate into (-1: skip)
 };
 
 struct UmmaShared {
@@ -61,11 +74,16 @@ struct UmmaShared {
   uint64_t empty[UMMA_MAX_STAGES];
   uint64_t tmem_full[2];
   uint64_t tmem_empty[2];
-  uint64_t idx_full[UMMA_IDX_SLOTS];
-  uint64_t idx_empty[UMMA_IDX_SLOTS];
+  uint64_t gidx_full[UMMA_IDX_SLOTS];
+  uint64_t gidx_empty[UMMA_IDX_SLOTS];
+  uint64_t sidx_full[UMMA_IDX_SLOTS];
+  uint64_t sidx_empty[UMMA_IDX_SLOTS];
+  uint64_t patch_full[2];
+  uint64_t patch_empty[2];
   uint32_t tmem_base;
   int abort_flag;
-  IdxSlot slot[UMMA_IDX_SLOTS];
+  GatherSlot gs[UMMA_IDX_SLOTS];
+  ScatterSlot ss[UMMA_IDX_SLOTS];
 };
 constexpr int UMMA_SHARED_BYTES = (sizeof(UmmaShared) + 255) & ~255;
 constexpr int UMMA_SMEM_FIXED = 1024 /* alignment slack */ + UMMA_SHARED_BYTES;
@@ -84,6 +102,7 @@ __device__ __forceinline__ uint32_t tmem_cols_pow2(uint32_t need) {
 __device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   int ok = 1;
   if ((threadIdx.x & 31) == 0) ok = umma::mbar_wait(umma::smem_u32(bar), parity, abort_flag) ? 1 : 0;
+  __syncwarp();  // orders the other lanes' later reads after what lane 0's acquire made visible
   return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 // the warp has finished with something: one arrival for all 32 lanes
@@ -92,19 +111,23 @@ __device__ __forceinline__ void warp_arrive(uint64_t* bar) {
   if ((threadIdx.x & 31) == 0) umma::mbar_arrive(umma::smem_u32(bar));
 }
 
-__device__ __forceinline__ void init_barriers(UmmaShared* sh, int n_stage, int idx_consumers) {
+__device__ __forceinline__ void init_barriers(UmmaShared* sh, int n_stage, int gidx_consumers, int sidx_consumers) {
   using namespace umma;
   for (int s = 0; s < n_stage; ++s) {
-    mbar_init(smem_u32(&sh->full[s]), UMMA_PROD_WARPS);
+    mbar_init(smem_u32(&sh->full[s]), UMMA_PROD_THREADS);  // one hardware arrival per producer thread
     mbar_init(smem_u32(&sh->empty[s]), 1);
   }
   for (int b = 0; b < 2; ++b) {
     mbar_init(smem_u32(&sh->tmem_full[b]), 1);
     mbar_init(smem_u32(&sh->tmem_empty[b]), UMMA_EPI_WARPS);
+    mbar_init(smem_u32(&sh->patch_full[b]), UMMA_EPI_WARPS);
+    mbar_init(smem_u32(&sh->patch_empty[b]), UMMA_SCATTER_WARPS);
   }
   for (int i = 0; i < UMMA_IDX_SLOTS; ++i) {
-    mbar_init(smem_u32(&sh->idx_full[i]), 1);
-    mbar_init(smem_u32(&sh->idx_empty[i]), idx_consumers);
+    mbar_init(smem_u32(&sh->gidx_full[i]), 1);
+    mbar_init(smem_u32(&sh->gidx_empty[i]), gidx_consumers);
+    mbar_init(smem_u32(&sh->sidx_full[i]), 1);
+    mbar_init(smem_u32(&sh->sidx_empty[i]), sidx_consumers > 0 ? sidx_consumers : 1);
   }
   sh->abort_flag = 0;
   mbar_fence_init();
@@ -123,7 +146,7 @@ __device__ __forceinline__ void load_kpos(const int32_t* __restrict__ kpos, int 
 //   D = [128 x n_dim] fp32 in TMEM, two buffers
 // =============================================================================================
 template <bool TF32, bool TRANS_W>
-__global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, int n_stage) {
+__global__ void __launch_bounds__(UMMA_GMS_THREADS, 1) umma_gms_kernel(GmsParams p, int n_stage, int n_patch) {
   using namespace umma;
   constexpr int ES = TF32 ? 4 : 2;
   constexpr int EPR = 128 / ES;  // elements per 128-byte span
@@ -132,7 +155,8 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
   const uint32_t w_bytes = (uint32_t)p.k_dim * p.n_dim * ES;
   uint8_t* sW = smem;
   uint8_t* sStage = smem + w_bytes;
-  UmmaShared* sh = reinterpret_cast<UmmaShared*>(sStage + (size_t)n_stage * UMMA_STAGE_BYTES);
+  uint8_t* sEpi = sStage + (size_t)n_stage * UMMA_STAGE_BYTES;
+  UmmaShared* sh = reinterpret_cast<UmmaShared*>(sEpi + (size_t)n_patch * UMMA_PATCH_BYTES);
   int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + UMMA_SHARED_BYTES);  // [k_vol + 2]
   int* kpos_s = tile_start + p.k_vol + 2;                                                         // [k_vol + 1]
 
@@ -142,7 +166,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
   const int kch = p.k_dim / EPR;  // 128-byte K chunks per row
   volatile int* abort_flag = &sh->abort_flag;
 
-  if (tid == 0) init_barriers(sh, n_stage, UMMA_PROD_WARPS + UMMA_EPI_WARPS);
+  if (tid == 0) init_barriers(sh, n_stage, UMMA_PROD_WARPS, UMMA_SCATTER_WARPS);
   load_kpos(p.kpos, p.k_vol, kpos_s);
   build_tile_table(UMMA_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
   const uint32_t tmem_cols = tmem_cols_pow2(2u * p.n_dim);
@@ -195,9 +219,11 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
         if (b < nb && ok) {
           const int i = tb + b - t0;
           const int sl = i % UMMA_IDX_SLOTS;
-          ok = warp_wait(&sh->idx_empty[sl], ((uint32_t)(i / UMMA_IDX_SLOTS) & 1u) ^ 1u, abort_flag);
+          const uint32_t par = ((uint32_t)(i / UMMA_IDX_SLOTS) & 1u) ^ 1u;
+          ok = warp_wait(&sh->gidx_empty[sl], par, abort_flag) && warp_wait(&sh->sidx_empty[sl], par, abort_flag);
           if (ok) {
-            IdxSlot* slot = &sh->slot[sl];
+            GatherSlot* gsl = &sh->gs[sl];
+            ScatterSlot* ssl = &sh->ss[sl];
 #pragma unroll
             for (int q = 0; q < 4; ++q) {
               const int row = lane + 32 * q;
@@ -206,20 +232,24 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
                 report_problem();  // a map entry outside the tensors: the pair is skipped
                 gv = sv = -1;
               }
-              slot->g[row] = gv;
-              slot->s[row] = sv;
+              gsl->g[row] = gv;
+              ssl->s[row] = sv;
             }
             if (lane == 0) {
-              slot->seg = seg_[b];
-              slot->widx = seg_[b] == p.k_vol ? p.dense_weight : seg_[b];
-              slot->cnt = cnt_[b];
+              gsl->seg = seg_[b];
+              gsl->widx = seg_[b] == p.k_vol ? p.dense_weight : seg_[b];
+              gsl->cnt = cnt_[b];
             }
-            warp_arrive(&sh->idx_full[sl]);
+            __syncwarp();
+            if (lane == 0) {
+              mbar_arrive(smem_u32(&sh->gidx_full[sl]));
+              mbar_arrive(smem_u32(&sh->sidx_full[sl]));
+            }
           }
         }
       }
     }
-  } else if (warp >= 5) {
+  } else if (warp >= 5 && warp <= 8) {
     // ------------------------------------------------------------------ producers
     const int tp = tid - UMMA_PROD_TID0;
     const int prow = tp >> 3, pc = tp & 7;
@@ -228,34 +258,23 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
     const uint8_t* wts = static_cast<const uint8_t*>(p.weights);
     const size_t src_row_bytes = (size_t)p.k_dim * ES;
     const uint32_t w_row_bytes = (uint32_t)p.c_out * ES;
-    int issued = 0, arrived = 0, cur_w = -1;
-
-    auto flush = [&]() {
-      cp_async_wait<0>();
-      fence_proxy_async();
-      __syncwarp();
-      while (arrived < issued) {
-        if (lane == 0) mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
-        ++arrived;
-      }
-    };
+    int issued = 0, cur_w = -1;
 
     for (int t = t0; t < t1 && ok; ++t) {
       const int i = t - t0;
       const int sl = i % UMMA_IDX_SLOTS;
-      ok = warp_wait(&sh->idx_full[sl], (uint32_t)(i / UMMA_IDX_SLOTS) & 1u, abort_flag);
+      ok = warp_wait(&sh->gidx_full[sl], (uint32_t)(i / UMMA_IDX_SLOTS) & 1u, abort_flag);
       if (!ok) break;
-      const IdxSlot* slot = &sh->slot[sl];
+      const GatherSlot* slot = &sh->gs[sl];
       const int widx = slot->widx;
       int g[8];
 #pragma unroll
       for (int q = 0; q < 8; ++q) g[q] = slot->g[prow + 16 * q];
-      warp_arrive(&sh->idx_empty[sl]);
+      warp_arrive(&sh->gidx_empty[sl]);
 
       const bool new_w = widx != cur_w;
       if (new_w) {
-        // the MMAs of everything issued so far read the old weights: let them finish first
-        flush();
+        // every MMA issued so far reads the old weights: wait until the last one has finished
         if (issued > 0) {
           const int last = issued - 1;
           ok = warp_wait(&sh->empty[last % n_stage], (uint32_t)(last / n_stage) & 1u, abort_flag);
@@ -298,17 +317,11 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
           const bool valid = g[q] >= 0;
           cp_async16(st + (uint32_t)q * 2048u, valid ? col + (size_t)g[q] * src_row_bytes : src, valid);
         }
-        cp_async_commit();
+        // the stage's "full" barrier hears from this thread when everything it has issued has landed
+        cp_async_arrive_noinc(smem_u32(&sh->full[s]));
         ++issued;
-        if (issued - arrived > UMMA_LOOKAHEAD) {
-          cp_async_wait<UMMA_LOOKAHEAD>();
-          fence_proxy_async();
-          warp_arrive(&sh->full[arrived % n_stage]);
-          ++arrived;
-        }
       }
     }
-    flush();
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t idesc = make_idesc(TF32, false, !TRANS_W, UMMA_TILE_M, p.n_dim);
@@ -324,8 +337,9 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
         const int s = it % n_stage;
         ok = warp_wait(&sh->full[s], (uint32_t)(it / n_stage) & 1u, abort_flag);
         if (!ok) break;
-        tc_fence_after();
         if (lane == 0) {
+          fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
+          tc_fence_after();
           const uint32_t sa = smem_u32(sStage + (size_t)s * UMMA_STAGE_BYTES);
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
@@ -346,67 +360,113 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_gms_kernel(GmsParams p, 
         __syncwarp();
       }
     }
-  } else {
-    // ------------------------------------------------------------------ epilogue (warps 0-3)
+  } else if (warp >= 10) {
+    // ------------------------------------------------------------------ scatter (warps 10-13)
+    // Warp w owns tile rows [32 w, 32 w + 32).  It reads a parked 256-byte block back so that `cpr`
+    // consecutive lanes cover one row, and adds it to the destination row with 16-byte vector reds.
+    const int sw_i = warp - 10;
     uint8_t* dst = static_cast<uint8_t*>(p.dst);
-    const size_t dst_row_bytes = (size_t)p.n_dim * ES;
+    const uint32_t row_bytes = (uint32_t)p.n_dim * ES;
+    uint32_t blk_i = 0;
     int tile_i = 0;
     for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
       const int sl = tile_i % UMMA_IDX_SLOTS;
-      ok = warp_wait(&sh->idx_full[sl], (uint32_t)(tile_i / UMMA_IDX_SLOTS) & 1u, abort_flag);
+      ok = warp_wait(&sh->sidx_full[sl], (uint32_t)(tile_i / UMMA_IDX_SLOTS) & 1u, abort_flag);
       if (!ok) break;
-      const int srow = sh->slot[sl].s[tid];
-      warp_arrive(&sh->idx_empty[sl]);
-
+      const int srow = sh->ss[sl].s[sw_i * 32 + lane];
+      warp_arrive(&sh->sidx_empty[sl]);
+      for (uint32_t cb = 0; cb < row_bytes && ok; cb += 256, ++blk_i) {
+        const uint32_t pb = blk_i % (uint32_t)n_patch;
+        ok = warp_wait(&sh->patch_full[pb], (blk_i / (uint32_t)n_patch) & 1u, abort_flag);
+        if (!ok) break;
+        const uint32_t blk_bytes = min(256u, row_bytes - cb);
+        const uint32_t cpr = blk_bytes >> 4;  // 16-byte chunks per row in this block: 8 or 16
+        const uint32_t rpi = 32 / cpr;        // rows one warp-wide instruction covers: 4 or 2
+        const uint32_t ch = lane % cpr, rsub = lane / cpr;
+        const uint8_t* patch = sEpi + pb * UMMA_PATCH_BYTES + (size_t)(sw_i * 32) * 256;
+        uint8_t* dcol = dst + cb + (ch << 4);
+#pragma unroll 1
+        for (uint32_t r0 = 0; r0 < 32; r0 += 8 * rpi) {  // cpr = 16: two rounds of 8 reds; cpr = 8: one
+          uint4 v[8];
+          int sr[8];
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            const uint32_t r = r0 + u * rpi + rsub;  // row within this warp's 32
+            v[u] = *reinterpret_cast<const uint4*>(patch + r * 256 + ((ch ^ (r & 7)) << 4));
+            sr[u] = __shfl_sync(0xffffffffu, srow, r);
+          }
+#pragma unroll
+          for (int u = 0; u < 8; ++u) {
+            if (sr[u] >= 0) {
+              uint8_t* o = dcol + (size_t)sr[u] * row_bytes;
+              if (TF32) red_add_v4(reinterpret_cast<float*>(o), __uint_as_float(v[u].x), __uint_as_float(v[u].y),
+                                   __uint_as_float(v[u].z), __uint_as_float(v[u].w));
+              else red_add_h8(reinterpret_cast<__half*>(o), v[u].x, v[u].y, v[u].z, v[u].w);
+            }
+          }
+        }
+        warp_arrive(&sh->patch_empty[pb]);  // every lane has its data in registers and has issued its reds
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ drain (warps 0-3)
+    // Each thread owns one accumulator row (its TMEM lane): it converts the row block by block
+    // (256 bytes of output at a time) and parks it, 16-byte chunks XOR-swizzled by row, in the patch.
+    const uint32_t row_bytes = (uint32_t)p.n_dim * ES;
+    int tile_i = 0;
+    uint32_t blk_i = 0;
+    for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
       const int buf = tile_i & 1;
       ok = warp_wait(&sh->tmem_full[buf], (uint32_t)(tile_i >> 1) & 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * p.n_dim;
-      uint8_t* drow = dst + (size_t)(srow < 0 ? 0 : srow) * dst_row_bytes;
-      for (int c0 = 0; c0 < p.n_dim; c0 += 64) {
-        // 64 columns at a time (n_dim is a multiple of 32)
-        const bool second = c0 + 32 < p.n_dim;
-        uint32_t v[4][16];
-        tmem_ld16(taddr + c0, v[0]);
-        tmem_ld16(taddr + c0 + 16, v[1]);
-        if (second) {
-          tmem_ld16(taddr + c0 + 32, v[2]);
-          tmem_ld16(taddr + c0 + 48, v[3]);
+      for (uint32_t cb = 0; cb < row_bytes && ok; cb += 256, ++blk_i) {
+        const uint32_t blk_bytes = min(256u, row_bytes - cb);
+        const uint32_t ncol = blk_bytes / ES;
+        const uint32_t col0 = cb / ES;
+        const uint32_t pb = blk_i % (uint32_t)n_patch;
+        ok = warp_wait(&sh->patch_empty[pb], ((blk_i / (uint32_t)n_patch) & 1u) ^ 1u, abort_flag);
+        if (!ok) break;
+        uint8_t* mine = sEpi + pb * UMMA_PATCH_BYTES + (size_t)tid * 256;
+        const uint32_t sw7 = (uint32_t)(tid & 7);
+        for (uint32_t c0 = 0; c0 < ncol; c0 += 32) {
+          uint32_t v0[16], v1[16];
+          tmem_ld16(taddr + col0 + c0, v0);
+          tmem_ld16(taddr + col0 + c0 + 16, v1);
+          tmem_ld_wait();
+          if (TF32) {
+            const uint32_t ch0 = c0 / 4;  // first 16-byte chunk of these 32 columns
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              *reinterpret_cast<uint4*>(mine + (((ch0 + q) ^ sw7) << 4)) = make_uint4(v0[4 * q], v0[4 * q + 1], v0[4 * q + 2], v0[4 * q + 3]);
+              *reinterpret_cast<uint4*>(mine + (((ch0 + 4 + q) ^ sw7) << 4)) = make_uint4(v1[4 * q], v1[4 * q + 1], v1[4 * q + 2], v1[4 * q + 3]);
+            }
+          } else {
+            const uint32_t ch0 = c0 / 8;
+            uint32_t h[16];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              h[q] = pack_half2(__uint_as_float(v0[2 * q]), __uint_as_float(v0[2 * q + 1]));
+              h[8 + q] = pack_half2(__uint_as_float(v1[2 * q]), __uint_as_float(v1[2 * q + 1]));
+            }
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              *reinterpret_cast<uint4*>(mine + (((ch0 + q) ^ sw7) << 4)) = make_uint4(h[4 * q], h[4 * q + 1], h[4 * q + 2], h[4 * q + 3]);
+          }
         }
-        tmem_ld_wait();
-        if (c0 + 64 >= p.n_dim) {
-          // accumulator fully read: hand the TMEM buffer back before the (slower) scatter
+        if (cb + 256 >= row_bytes) {
+          // accumulator fully read: hand the TMEM buffer back
           tc_fence_before();
           warp_arrive(&sh->tmem_empty[buf]);
         }
-        if (srow >= 0) {
-#pragma unroll
-          for (int h = 0; h < 4; ++h) {
-            if (h < 2 || second) {
-              if (TF32) {
-                float* o = reinterpret_cast<float*>(drow) + c0 + 16 * h;
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  red_add_v4(o + 4 * q, __uint_as_float(v[h][4 * q]), __uint_as_float(v[h][4 * q + 1]),
-                             __uint_as_float(v[h][4 * q + 2]), __uint_as_float(v[h][4 * q + 3]));
-              } else {
-                __half* o = reinterpret_cast<__half*>(drow) + c0 + 16 * h;
-                uint32_t hh[8];
-#pragma unroll
-                for (int q = 0; q < 8; ++q) hh[q] = pack_half2(__uint_as_float(v[h][2 * q]), __uint_as_float(v[h][2 * q + 1]));
-                red_add_h8(o, hh[0], hh[1], hh[2], hh[3]);
-                red_add_h8(o + 8, hh[4], hh[5], hh[6], hh[7]);
-              }
-            }
-          }
-        }
+        warp_arrive(&sh->patch_full[pb]);
       }
     }
   }
 
   if (!ok && lane == 0) report_problem();
-  cp_async_wait<0>();
+  cp_async_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 4) tmem_dealloc(tmem_base, tmem_cols);
@@ -451,7 +511,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
   const uint32_t lbo = (uint32_t)tl.pb * 128u;  // next 128 bytes of every gathered row
   const uint32_t buf_cols = (uint32_t)tl.n_mtile * p.c_out;
 
-  if (tid == 0) init_barriers(sh, n_stage, UMMA_PROD_WARPS + 1);
+  if (tid == 0) init_barriers(sh, n_stage, UMMA_PROD_WARPS + 1, 0);
   load_kpos(p.kpos, p.k_vol, kpos_s);
   build_tile_table(tl.pb, p.kpos, p.k_vol, 0, tile_start);
   const uint32_t tmem_cols = tmem_cols_pow2(buf_cols * tl.n_buf);
@@ -501,9 +561,9 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
         if (b < nb && ok) {
           const int i = tb + b - t0;
           const int sl = i % UMMA_IDX_SLOTS;
-          ok = warp_wait(&sh->idx_empty[sl], ((uint32_t)(i / UMMA_IDX_SLOTS) & 1u) ^ 1u, abort_flag);
+          ok = warp_wait(&sh->gidx_empty[sl], ((uint32_t)(i / UMMA_IDX_SLOTS) & 1u) ^ 1u, abort_flag);
           if (ok) {
-            IdxSlot* slot = &sh->slot[sl];
+            GatherSlot* slot = &sh->gs[sl];
 #pragma unroll
             for (int q = 0; q < 2; ++q) {
               const int row = lane + 32 * q;
@@ -513,13 +573,13 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
                 a = o = -1;
               }
               slot->g[row] = a;
-              slot->s[row] = o;
+              slot->g[UMMA_WG_MAX_PB + row] = o;
             }
             if (lane == 0) {
               slot->seg = seg_[b];
               slot->cnt = cnt_[b];
             }
-            warp_arrive(&sh->idx_full[sl]);
+            warp_arrive(&sh->gidx_full[sl]);
           }
         }
       }
@@ -532,46 +592,55 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
     const int ca = p.c_in * ES / 16, cb = p.c_out * ES / 16;  // 16-byte chunks per row
     const int total_a = tl.pb * ca, total_b = tl.pb * cb;
     const size_t a_row_bytes = (size_t)p.c_in * ES, b_row_bytes = (size_t)p.c_out * ES;
-    int issued = 0, arrived = 0;
+    // Thread tp handles the 16-byte chunks e = tp, tp + 128, tp + 256 ... of a stage, chunk e being
+    // (row e / cpr, column chunk e % cpr).  The walk is kept as a (row, chunk) pair advanced by a
+    // constant step, so the loop has no division.
+    const int a_r0 = tp / ca, a_c0 = tp % ca, a_dr = UMMA_PROD_THREADS / ca, a_dc = UMMA_PROD_THREADS % ca;
+    const int b_r0 = tp / cb, b_c0 = tp % cb, b_dr = UMMA_PROD_THREADS / cb, b_dc = UMMA_PROD_THREADS % cb;
+
+    // gathers `total` chunks of rows idx[row] (cpr chunks each) into an MN-major operand at `sdst`
+    auto gather_rows = [&](uint32_t sdst, const uint8_t* gsrc, size_t row_bytes, const int* idx, int total, int cpr,
+                           int r0, int c0, int dr, int dc) {
+      int r = r0, c = c0;
+      for (int e = tp; e < total; e += 4 * UMMA_PROD_THREADS) {
+        int rr[4], cc[4], ix[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          rr[u] = r;
+          cc[u] = c;
+          ix[u] = (e + u * UMMA_PROD_THREADS < total) ? idx[r] : -2;
+          c += dc;
+          r += dr;
+          if (c >= cpr) { c -= cpr; ++r; }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (ix[u] != -2) {
+            const uint32_t off = TF32 ? mnmajor32_offset((uint32_t)rr[u], (uint32_t)cc[u] * 16u, lbo, 512u)
+                                      : mnmajor_offset((uint32_t)rr[u], (uint32_t)cc[u] * 16u, lbo, 1024u);
+            const bool valid = ix[u] >= 0;
+            cp_async16(sdst + off, valid ? gsrc + ((size_t)ix[u] * row_bytes + (size_t)cc[u] * 16u) : gsrc, valid);
+          }
+        }
+      }
+    };
+
+    int issued = 0;
     for (int t = t0; t < t1 && ok; ++t) {
       const int i = t - t0;
       const int sl = i % UMMA_IDX_SLOTS;
-      ok = warp_wait(&sh->idx_full[sl], (uint32_t)(i / UMMA_IDX_SLOTS) & 1u, abort_flag);
+      ok = warp_wait(&sh->gidx_full[sl], (uint32_t)(i / UMMA_IDX_SLOTS) & 1u, abort_flag);
       if (!ok) break;
-      const IdxSlot* slot = &sh->slot[sl];
+      const GatherSlot* slot = &sh->gs[sl];
       const int s = issued % n_stage;
       ok = warp_wait(&sh->empty[s], ((uint32_t)(issued / n_stage) & 1u) ^ 1u, abort_flag);
       if (!ok) break;
       const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
-      const uint32_t sb = sa + a_bytes;
-      for (int e = tp; e < total_a; e += UMMA_PROD_THREADS) {
-        const uint32_t row = e / ca, c = e % ca;
-        const int a = slot->g[row];
-        const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
-        cp_async16(sa + off, a >= 0 ? feats + ((size_t)a * a_row_bytes + c * 16u) : feats, a >= 0);
-      }
-      for (int e = tp; e < total_b; e += UMMA_PROD_THREADS) {
-        const uint32_t row = e / cb, c = e % cb;
-        const int o = slot->s[row];
-        const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
-        cp_async16(sb + off, o >= 0 ? og + ((size_t)o * b_row_bytes + c * 16u) : og, o >= 0);
-      }
-      cp_async_commit();
-      warp_arrive(&sh->idx_empty[sl]);
+      gather_rows(sa, feats, a_row_bytes, slot->g, total_a, ca, a_r0, a_c0, a_dr, a_dc);
+      gather_rows(sa + a_bytes, og, b_row_bytes, slot->g + UMMA_WG_MAX_PB, total_b, cb, b_r0, b_c0, b_dr, b_dc);
+      cp_async_arrive_noinc(smem_u32(&sh->full[s]));
+      warp_arrive(&sh->gidx_empty[sl]);
       ++issued;
-      if (issued - arrived > UMMA_LOOKAHEAD) {
-        cp_async_wait<UMMA_LOOKAHEAD>();
-        fence_proxy_async();
-        warp_arrive(&sh->full[arrived % n_stage]);
-        ++arrived;
-      }
-    }
-    cp_async_wait<0>();
-    fence_proxy_async();
-    __syncwarp();
-    while (arrived < issued) {
-      if (lane == 0) mbar_arrive(smem_u32(&sh->full[arrived % n_stage]));
-      ++arrived;
     }
   } else if (warp == 4) {
     // ------------------------------------------------------------------ MMA issuer
@@ -583,10 +652,10 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
     bool first = true;
     for (int t = t0; t < t1 && ok; ++t, ++it) {
       const int sl = it % UMMA_IDX_SLOTS;
-      ok = warp_wait(&sh->idx_full[sl], (uint32_t)(it / UMMA_IDX_SLOTS) & 1u, abort_flag);
+      ok = warp_wait(&sh->gidx_full[sl], (uint32_t)(it / UMMA_IDX_SLOTS) & 1u, abort_flag);
       if (!ok) break;
-      const int seg = sh->slot[sl].seg;
-      warp_arrive(&sh->idx_empty[sl]);
+      const int seg = sh->gs[sl].seg;
+      warp_arrive(&sh->gidx_empty[sl]);
       if (seg != cur_seg) {
         if (cur_seg >= 0) {
           if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[(run_i % tl.n_buf)]));
@@ -605,8 +674,9 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
       const int s = it % n_stage;
       ok = warp_wait(&sh->full[s], (uint32_t)(it / n_stage) & 1u, abort_flag);
       if (!ok) break;
-      tc_fence_after();
       if (lane == 0) {
+        fence_proxy_async();
+        tc_fence_after();
         const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
         const uint32_t sb = sa + a_bytes;
         for (int ks = 0; ks < tl.pb / UK; ++ks) {
@@ -673,7 +743,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
   }
 
   if (!ok && lane == 0) report_problem();
-  cp_async_wait<0>();
+  cp_async_wait_all();
   tc_fence_before();
   __syncthreads();
   if (warp == 4) tmem_dealloc(tmem_base, tmem_cols);
@@ -705,17 +775,22 @@ inline int launch_umma_gms(const GmsParams& p, bool trans, bool f16, cudaStream_
   if (!aligned16(p.src) || !aligned16(p.weights) || !aligned16(p.dst)) return 1;
   const int w_bytes = p.k_dim * p.n_dim * es;
   const int fixed = UMMA_SMEM_FIXED + umma_table_bytes(p.k_vol);
-  int n_stage = (max_smem - fixed - w_bytes) / UMMA_STAGE_BYTES;
+  int n_patch = UMMA_MAX_PATCHES;
+  int n_stage = (max_smem - fixed - w_bytes - n_patch * UMMA_PATCH_BYTES) / UMMA_STAGE_BYTES;
+  if (n_stage < 4) {  // large weight tiles: give the second patch's room to the gather stages
+    n_patch = 1;
+    n_stage = (max_smem - fixed - w_bytes - n_patch * UMMA_PATCH_BYTES) / UMMA_STAGE_BYTES;
+  }
   if (n_stage > UMMA_MAX_STAGES) n_stage = UMMA_MAX_STAGES;
-  if (n_stage <= UMMA_LOOKAHEAD) return 1;
-  const int smem = fixed + w_bytes + n_stage * UMMA_STAGE_BYTES;
+  if (n_stage < 2) return 1;
+  const int smem = fixed + w_bytes + n_patch * UMMA_PATCH_BYTES + n_stage * UMMA_STAGE_BYTES;
   int rc;
   if (f16) {
-    if (trans) { rc = ensure_smem(umma_gms_kernel<false, true>, max_smem, 0); if (rc) return rc; umma_gms_kernel<false, true><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
-    else       { rc = ensure_smem(umma_gms_kernel<false, false>, max_smem, 1); if (rc) return rc; umma_gms_kernel<false, false><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+    if (trans) { rc = ensure_smem(umma_gms_kernel<false, true>, max_smem, 0); if (rc) return rc; umma_gms_kernel<false, true><<<sms, UMMA_GMS_THREADS, smem, st>>>(p, n_stage, n_patch); }
+    else       { rc = ensure_smem(umma_gms_kernel<false, false>, max_smem, 1); if (rc) return rc; umma_gms_kernel<false, false><<<sms, UMMA_GMS_THREADS, smem, st>>>(p, n_stage, n_patch); }
   } else {
-    if (trans) { rc = ensure_smem(umma_gms_kernel<true, true>, max_smem, 2); if (rc) return rc; umma_gms_kernel<true, true><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
-    else       { rc = ensure_smem(umma_gms_kernel<true, false>, max_smem, 3); if (rc) return rc; umma_gms_kernel<true, false><<<sms, UMMA_THREADS, smem, st>>>(p, n_stage); }
+    if (trans) { rc = ensure_smem(umma_gms_kernel<true, true>, max_smem, 2); if (rc) return rc; umma_gms_kernel<true, true><<<sms, UMMA_GMS_THREADS, smem, st>>>(p, n_stage, n_patch); }
+    else       { rc = ensure_smem(umma_gms_kernel<true, false>, max_smem, 3); if (rc) return rc; umma_gms_kernel<true, false><<<sms, UMMA_GMS_THREADS, smem, st>>>(p, n_stage, n_patch); }
   }
   return 0;
 }
@@ -739,7 +814,7 @@ inline bool wgrad_tiling(int c_in, int c_out, int es, int max_smem, int k_vol, W
   tl->pb = pb;
   int n_stage = (max_smem - UMMA_SMEM_FIXED - umma_table_bytes(k_vol)) / (pb * row_bytes);
   if (n_stage > UMMA_MAX_STAGES) n_stage = UMMA_MAX_STAGES;
-  if (n_stage <= UMMA_LOOKAHEAD) return false;
+  if (n_stage < 2) return false;
   tl->n_stage = n_stage;
   return true;
 }
