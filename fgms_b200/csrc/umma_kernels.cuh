@@ -6,12 +6,14 @@
 //   warps 0-3  drain      tcgen05.ld of the fp32 accumulators, conversion to the storage type, parked in a
 //                         swizzled shared-memory patch (wgrad: straight to vector red.global.add.f32)
 //   warp  4    MMA        one thread issues tcgen05.mma / tcgen05.commit; owns the TMEM allocation
-//   warps 5-8  producers  gather rows with 16-byte cp.async straight into the 128-byte-swizzled
-//                         operand layout tcgen05 reads (no staging copy, no register round trip)
-//   warp  9    index      streams the kernel-map entries of upcoming tiles (coalesced, bounds-checked)
+//   warps 5-12 producers  gather rows with 16-byte cp.async straight into the 128-byte-swizzled
+//                         operand layout tcgen05 reads (no staging copy, no register round trip);
+//                         eight warps because the load/store unit moves about 5 bytes per cycle per
+//                         issuing warp for such gathers (measured: 20 B/cycle/SM with 4 warps, 40 with 8)
+//   warp  13   index      streams the kernel-map entries of upcoming tiles (coalesced, bounds-checked)
 //                         into a small shared-memory ring, several tiles ahead of everyone else, so
 //                         that no other role ever waits on a dependent global load
-//   warps 10-13 scatter   (forward / dgrad) read the patch back so that 8 or 16 consecutive lanes cover one
+//   warps 14-17 scatter   (forward / dgrad) read the patch back so that 8 or 16 consecutive lanes cover one
 //                         destination row and issue vector red.global.add.  The SM's reduction path tops
 //                         out near 25 bytes per cycle (measured); four warps that alternate between
 //                         reading the patch and issuing reds get within about 20 % of it
@@ -34,18 +36,21 @@
 
 namespace fgms {
 
-constexpr int UMMA_THREADS = 320;       // wgrad: warps 0-9
-constexpr int UMMA_GMS_THREADS = 448;   // forward / dgrad: four more warps for the scatter
+constexpr int UMMA_THREADS = 448;       // wgrad: warps 0-13
+constexpr int UMMA_GMS_THREADS = 576;   // forward / dgrad: four more warps for the scatter
 constexpr int UMMA_SCATTER_WARPS = 4;
-constexpr int UMMA_PROD_THREADS = 128;
-constexpr int UMMA_PROD_TID0 = 160;
-constexpr int UMMA_PROD_WARPS = 4;
+constexpr int UMMA_PROD_WARPS = 8;
+constexpr int UMMA_PROD_THREADS = UMMA_PROD_WARPS * 32;
+constexpr int UMMA_PROD_WARP0 = 5;
+constexpr int UMMA_PROD_TID0 = UMMA_PROD_WARP0 * 32;
+constexpr int UMMA_IDX_WARP = UMMA_PROD_WARP0 + UMMA_PROD_WARPS;   // 13
+constexpr int UMMA_SCATTER_WARP0 = UMMA_IDX_WARP + 1;              // 14
 constexpr int UMMA_EPI_WARPS = 4;
 constexpr int UMMA_TILE_M = 128;      // pairs per forward / dgrad tile
 constexpr int UMMA_STAGE_BYTES = 16384;
 constexpr int UMMA_MAX_STAGES = 8;
 constexpr int UMMA_IDX_SLOTS = 16;    // index-ring depth (tiles the index warp may run ahead)
-constexpr int UMMA_IDX_BATCH = 8;     // tiles whose map entries the index warp loads at once
+constexpr int UMMA_IDX_BATCH = 4;     // tiles whose map entries the index warp loads at once
 constexpr int UMMA_WG_MAX_PB = 64;    // pairs per wgrad stage, at most
 constexpr int UMMA_PATCH_BYTES = UMMA_TILE_M * 256;  // one 256-byte block of every row of a tile
 constexpr int UMMA_MAX_PATCHES = 2;  // patches are filled and scattered alternately when two fit
@@ -183,7 +188,7 @@ __global__ void __launch_bounds__(UMMA_GMS_THREADS, 1) umma_gms_kernel(GmsParams
   cta_tile_range(tile_start[n_seg], &t0, &t1);
   bool ok = true;
 
-  if (warp == 9) {
+  if (warp == UMMA_IDX_WARP) {
     // ------------------------------------------------------------------ index warp
     for (int tb = t0; tb < t1 && ok; tb += UMMA_IDX_BATCH) {
       const int nb = min(UMMA_IDX_BATCH, t1 - tb);
@@ -249,10 +254,10 @@ __global__ void __launch_bounds__(UMMA_GMS_THREADS, 1) umma_gms_kernel(GmsParams
         }
       }
     }
-  } else if (warp >= 5 && warp <= 8) {
+  } else if (warp >= UMMA_PROD_WARP0 && warp < UMMA_IDX_WARP) {
     // ------------------------------------------------------------------ producers
     const int tp = tid - UMMA_PROD_TID0;
-    const int prow = tp >> 3, pc = tp & 7;
+    const int prow = tp >> 3, pc = tp & 7;  // thread gathers chunk pc of rows prow, prow + 32, prow + 64, prow + 96
     const uint32_t a_dst0 = (uint32_t)(prow >> 3) * 1024u + (uint32_t)(prow & 7) * 128u + (uint32_t)((pc ^ (prow & 7)) << 4);
     const uint8_t* src = static_cast<const uint8_t*>(p.src);
     const uint8_t* wts = static_cast<const uint8_t*>(p.weights);
@@ -267,9 +272,9 @@ __global__ void __launch_bounds__(UMMA_GMS_THREADS, 1) umma_gms_kernel(GmsParams
       if (!ok) break;
       const GatherSlot* slot = &sh->gs[sl];
       const int widx = slot->widx;
-      int g[8];
+      int g[4];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) g[q] = slot->g[prow + 16 * q];
+      for (int q = 0; q < 4; ++q) g[q] = slot->g[prow + 32 * q];
       warp_arrive(&sh->gidx_empty[sl]);
 
       const bool new_w = widx != cur_w;
@@ -313,9 +318,9 @@ __global__ void __launch_bounds__(UMMA_GMS_THREADS, 1) umma_gms_kernel(GmsParams
         const uint32_t st = smem_u32(sStage + (size_t)s * UMMA_STAGE_BYTES) + a_dst0;
         const uint8_t* col = src + (size_t)kc * 128 + (size_t)pc * 16;
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
+        for (int q = 0; q < 4; ++q) {
           const bool valid = g[q] >= 0;
-          cp_async16(st + (uint32_t)q * 2048u, valid ? col + (size_t)g[q] * src_row_bytes : src, valid);
+          cp_async16(st + (uint32_t)q * 4096u, valid ? col + (size_t)g[q] * src_row_bytes : src, valid);
         }
         // the stage's "full" barrier hears from this thread when everything it has issued has landed
         cp_async_arrive_noinc(smem_u32(&sh->full[s]));
@@ -360,11 +365,11 @@ __global__ void __launch_bounds__(UMMA_GMS_THREADS, 1) umma_gms_kernel(GmsParams
         __syncwarp();
       }
     }
-  } else if (warp >= 10) {
-    // ------------------------------------------------------------------ scatter (warps 10-13)
+  } else if (warp >= UMMA_SCATTER_WARP0) {
+    // ------------------------------------------------------------------ scatter (warps 14-17)
     // Warp w owns tile rows [32 w, 32 w + 32).  It reads a parked 256-byte block back so that `cpr`
     // consecutive lanes cover one row, and adds it to the destination row with 16-byte vector reds.
-    const int sw_i = warp - 10;
+    const int sw_i = warp - UMMA_SCATTER_WARP0;
     uint8_t* dst = static_cast<uint8_t*>(p.dst);
     const uint32_t row_bytes = (uint32_t)p.n_dim * ES;
     uint32_t blk_i = 0;
@@ -528,7 +533,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
   cta_tile_range(tile_start[n_seg], &t0, &t1);
   bool ok = true;
 
-  if (warp == 9) {
+  if (warp == UMMA_IDX_WARP) {
     // ------------------------------------------------------------------ index warp (pb <= 64 pairs per stage)
     for (int tb = t0; tb < t1 && ok; tb += UMMA_IDX_BATCH) {
       const int nb = min(UMMA_IDX_BATCH, t1 - tb);
@@ -584,7 +589,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
         }
       }
     }
-  } else if (warp >= 5) {
+  } else if (warp >= UMMA_PROD_WARP0 && warp < UMMA_IDX_WARP) {
     // ------------------------------------------------------------------ producers
     const int tp = tid - UMMA_PROD_TID0;
     const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
@@ -592,7 +597,7 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
     const int ca = p.c_in * ES / 16, cb = p.c_out * ES / 16;  // 16-byte chunks per row
     const int total_a = tl.pb * ca, total_b = tl.pb * cb;
     const size_t a_row_bytes = (size_t)p.c_in * ES, b_row_bytes = (size_t)p.c_out * ES;
-    // Thread tp handles the 16-byte chunks e = tp, tp + 128, tp + 256 ... of a stage, chunk e being
+    // Thread tp handles the 16-byte chunks e = tp, tp + 256, tp + 512 ... of a stage, chunk e being
     // (row e / cpr, column chunk e % cpr).  The walk is kept as a (row, chunk) pair advanced by a
     // constant step, so the loop has no division.
     const int a_r0 = tp / ca, a_c0 = tp % ca, a_dr = UMMA_PROD_THREADS / ca, a_dc = UMMA_PROD_THREADS % ca;

@@ -1,0 +1,107 @@
+"""Multi-GPU host logic on CPU ranks: pair sharding by row range and the weight-gradient exchange
+(gloo, world_size 2).  No GPU is involved; the per-rank compute is the oracle."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from fgms_b200 import clouds, maps
+from fgms_b200.dist import allreduce_sum_, balanced_row_ranges, shard_pairs_by_rows
+from oracle import spconv_oracle as orc
+
+
+def _problem():
+    coords = clouds.surface_cloud(2500, 40, 31)
+    km = maps.build_submanifold_map(coords)
+    f, w, g = clouds.make_tensors(km.n_in, km.n_out, 12, 20, km.k_vol, 31)
+    return km, f, w, g
+
+
+@pytest.mark.parametrize("world", [1, 2, 3, 8])
+@pytest.mark.parametrize("by", ["out", "in"])
+def test_shards_partition_the_pairs_and_own_disjoint_rows(world, by):
+    km, f, w, g = _problem()
+    shards, bounds = shard_pairs_by_rows(km, world, by)
+    assert bounds[0] == 0 and bounds[-1] == (km.n_out if by == "out" else km.n_in)
+    assert sum(s.pairs for s in shards) == km.pairs
+    for r, s in enumerate(shards):
+        s.validate()
+        key = s.omap if by == "out" else s.imap
+        if key.size:
+            assert bounds[r] <= key.min() and key.max() < bounds[r + 1]
+        # order inside every offset is preserved
+        for k in range(km.k_vol):
+            a, b = s.kpos[k], s.kpos[k + 1]
+            assert (np.diff(s.omap[a:b]) > 0).all()
+    sizes = np.array([s.pairs for s in shards])
+    assert sizes.max() - sizes.min() <= 0.15 * km.pairs / world + 64  # balanced by pair count
+
+
+def test_sharded_forward_and_dgrad_need_no_exchange():
+    km, f, w, g = _problem()
+    full_out = orc.fwd(f, w, km.n_out, km.kpos, km.imap, km.omap)
+    shards, bounds = shard_pairs_by_rows(km, 4, "out")
+    out = np.zeros_like(full_out)
+    for r, s in enumerate(shards):
+        part = orc.fwd(f, w, km.n_out, s.kpos, s.imap, s.omap)
+        assert np.abs(part[: bounds[r]]).max(initial=0) == 0 and np.abs(part[bounds[r + 1]:]).max(initial=0) == 0
+        out[bounds[r]: bounds[r + 1]] = part[bounds[r]: bounds[r + 1]]  # each rank owns its rows outright
+    assert np.array_equal(out, full_out)
+    full_ig = orc.dgrad(g, w, km.n_in, km.kpos, km.imap, km.omap)
+    shards, bounds = shard_pairs_by_rows(km, 4, "in")
+    ig = np.zeros_like(full_ig)
+    for r, s in enumerate(shards):
+        ig[bounds[r]: bounds[r + 1]] = orc.dgrad(g, w, km.n_in, s.kpos, s.imap, s.omap)[bounds[r]: bounds[r + 1]]
+    assert np.array_equal(ig, full_ig)
+
+
+def test_balanced_ranges_edge_cases():
+    assert balanced_row_ranges(np.zeros(0, np.int32), 10, 4).tolist() == [0, 0, 0, 0, 10]
+    b = balanced_row_ranges(np.array([5] * 100, np.int32), 10, 2)  # all pairs on one row
+    assert b[0] == 0 and b[-1] == 10 and (np.diff(b) >= 0).all()
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _rank_main(rank, world, port, q):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        km, f, w, g = _problem()
+        shards, _ = shard_pairs_by_rows(km, world, "out")
+        s = shards[rank]
+        part = torch.from_numpy(orc.wgrad(f, g, km.k_vol, s.kpos, s.imap, s.omap))  # this rank's partial sums
+        allreduce_sum_(part)                                                        # the one exchange step
+        ref = orc.wgrad(f, g, km.k_vol, km.kpos, km.imap, km.omap)
+        q.put((rank, float(np.abs(part.numpy() - ref).max()), float(np.abs(ref).max())))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_weight_gradient_allreduce_two_ranks():
+    world, port = 2, _free_port()
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_rank_main, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    for rank, err, scale in results:
+        assert err <= 1e-12 * max(scale, 1.0), (rank, err)
+
+
+def test_allreduce_is_a_noop_without_a_process_group():
+    t = torch.ones(4)
+    assert allreduce_sum_(t) is t and t.sum() == 4
