@@ -24,6 +24,7 @@ SIGNATURES = {
     "fgms_b200_dgrad": (c_int, [c_void_p] * 6 + [c_int] * 7 + [c_void_p]),
     "fgms_b200_wgrad": (c_int, [c_void_p] * 6 + [c_int] * 7 + [c_void_p, c_size_t, c_int, c_void_p]),
     "fgms_b200_wgrad_finalize": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
+    "fgms_b200_wgrad_f16_noalloc": (c_int, [c_void_p] * 6 + [c_int] * 6 + [c_void_p]),
     "fgms_b200_wgrad_workspace_bytes": (c_size_t, [c_int] * 4),
     "fgms_b200_bwd": (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_int64] + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
     "fgms_b200_kernel_family": (c_int, [c_int] * 5),

@@ -23,7 +23,7 @@ import torch
 from . import _lib
 
 __all__ = ["fgms_fusion_fwd_cuda", "fgms_fwd_cuda", "fgms_bwd_cuda", "fgms_dgrad_cuda", "fgms_wgrad_cuda",
-           "wgrad_workspace", "wgrad_finalize", "kernel_family", "device_status", "launch_count"]
+           "wgrad_workspace", "wgrad_finalize", "fgms_wgrad_noalloc_cuda", "kernel_family", "device_status", "launch_count"]
 
 _L = _lib.lib
 
@@ -189,6 +189,33 @@ def fgms_wgrad_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map, out_map
             _ptr(workspace), workspace.numel() * 4 if workspace is not None else 0, int(bool(accumulate)),
             _stream()))
     return workspace
+
+
+NOALLOC_MAX_ELEMS = 512 * 1024  # FGMS_NOALLOC_MAX_ELEMS in include/fgms_b200.h
+
+
+def fgms_wgrad_noalloc_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map, out_map, arch80=True):
+    """fp16 weight gradient through the allocation-free entry point of the library.
+
+    For callers that must not (or cannot) allocate device memory when they call — a serving thread
+    where ``cudaMalloc`` is off limits, a process whose memory pool is fully handed out, a thin
+    binding with no allocator.  Same result as ``fgms_wgrad_cuda``; the fp32 partial sums use a
+    fixed 2 MiB array inside the library, so ``k_vol * c_in * c_out`` may not exceed
+    ``NOALLOC_MAX_ELEMS`` (``ValueError`` otherwise).  Calls on one device share that array: do not
+    let two of them overlap on the GPU, and make the first call on a device outside stream capture."""
+    k_vol = kernel_grad.size(0)
+    _check_feat("in_feats", in_feats, torch.float16)
+    _check_feat("out_feats_grad", out_feats_grad, torch.float16)
+    _check_feat("kernel_grad", kernel_grad, torch.float16, dim=3)
+    _check_index("kpos", kpos, in_feats.device, k_vol + 1)
+    _check_index("in_map", in_map, in_feats.device)
+    _check_index("out_map", out_map, in_feats.device)
+    _, math = _dtype_math(in_feats, arch80)
+    with torch.cuda.device(in_feats.device):
+        _lib.check(_L.fgms_b200_wgrad_f16_noalloc(
+            _ptr(in_feats), _ptr(out_feats_grad), _ptr(kernel_grad), _ptr(kpos), _ptr(in_map), _ptr(out_map),
+            in_feats.size(0), out_feats_grad.size(0), kernel_grad.size(1), kernel_grad.size(2), k_vol, math,
+            _stream()))
 
 
 def wgrad_finalize(kernel_grad: torch.Tensor, partial_f32: torch.Tensor) -> None:

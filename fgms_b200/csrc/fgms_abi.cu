@@ -288,6 +288,47 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   return FGMS_OK;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Allocation-free weight gradient (see the header for who needs it).  The fp32 partial sums live
+// in this file-scope device array.  In host code `g_noalloc_scratch` is only a handle for the
+// symbol, not a device address: the address is looked up once per device with
+// cudaGetSymbolAddress while that device is current, and that pointer is what kernels get.
+// ---------------------------------------------------------------------------------------------
+static __device__ __align__(256) float g_noalloc_scratch[FGMS_NOALLOC_MAX_ELEMS];
+
+static int noalloc_scratch(float** out) {
+  static float* cached[64] = {};  // per device ordinal
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return fail(FGMS_ERR_CUDA, "device ordinal %d out of range", dev);
+  if (!cached[dev]) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_noalloc_scratch);  // `dev` is current: this is ITS copy of the array
+    if (e != cudaSuccess || !p) return fail(FGMS_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    cached[dev] = static_cast<float*>(p);
+  }
+  *out = cached[dev];
+  return FGMS_OK;
+}
+
+int fgms_b200_wgrad_f16_noalloc(const void* in_feats, const void* out_grad, void* kernel_grad,
+                                const int32_t* kpos, const int32_t* in_map, const int32_t* out_map,
+                                int n_in, int n_out, int c_in, int c_out, int k_vol, int math,
+                                void* stream) {
+  if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
+  const long long elems = (long long)k_vol * c_in * c_out;
+  if (elems > (long long)FGMS_NOALLOC_MAX_ELEMS)
+    return fail(FGMS_ERR_WORKSPACE,
+                "k_vol*c_in*c_out = %lld exceeds the %d fp32 values of the built-in scratch array; "
+                "call fgms_b200_wgrad with a workspace instead", elems, (int)FGMS_NOALLOC_MAX_ELEMS);
+  float* scratch = nullptr;
+  if (int rc = noalloc_scratch(&scratch)) return rc;
+  // fgms_b200_wgrad clears the first `elems` values itself (cudaMemsetAsync on `stream`)
+  return fgms_b200_wgrad(in_feats, out_grad, kernel_grad, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
+                         k_vol, FGMS_DTYPE_F16, math, scratch, (size_t)elems * sizeof(float), 1, stream);
+}
+
 int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel, void* in_grad,
                   void* kernel_grad, const int32_t* kpos, const int32_t* qkpos,
                   const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,

@@ -105,6 +105,28 @@ int fgms_b200_wgrad_finalize(void* kernel_grad_f16, const void* workspace_f32, i
 
 size_t fgms_b200_wgrad_workspace_bytes(int c_in, int c_out, int k_vol, int dtype);
 
+/* Weight gradient for fp16 storage that allocates nothing and needs no caller workspace.
+ * This entry point has no counterpart in the reference.  It exists for callers that cannot
+ * obtain device memory at the time of the call: code running under a memory pool that is already
+ * handed out in full, real-time or inference-server threads in which cudaMalloc (a call that may
+ * synchronise the whole device) is forbidden, and language bindings that own no allocator at all.
+ * It computes exactly what fgms_b200_wgrad computes with accumulate_into_kernel_grad = 1, but the
+ * fp32 partial sums live in a fixed array inside the library's device image instead of a
+ * caller-provided workspace.
+ *   - Limit: k_vol * c_in * c_out <= FGMS_NOALLOC_MAX_ELEMS (2 MiB of fp32; 27 x 128 x 128 fits,
+ *     27 x 256 x 128 does not).  Larger shapes are refused with FGMS_ERR_WORKSPACE; use
+ *     fgms_b200_wgrad with a workspace for those.  Every GPU that loads the library holds the
+ *     2 MiB array until the process exits.
+ *   - The first call on each device looks up the array's device address (no allocation).  Make that
+ *     first call outside any stream capture.
+ *   - All calls on one device share the array; it is cleared at the start of every call.  Two calls
+ *     that can overlap on the GPU (different streams, no dependency) race on it: serialise them. */
+#define FGMS_NOALLOC_MAX_ELEMS (512 * 1024)
+int fgms_b200_wgrad_f16_noalloc(const void* in_feats, const void* out_grad, void* kernel_grad,
+                                const int32_t* kpos, const int32_t* in_map, const int32_t* out_map,
+                                int n_in, int n_out, int c_in, int c_out, int k_vol, int math,
+                                void* stream);
+
 /* Both gradients.  Replaces ConvolutionBackward (backend/spconv.cu:414-571; Python name
  * fgms_bwd_cuda).  separate_mid is accepted and ignored, as in the reference. */
 int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel, void* in_grad,
