@@ -597,38 +597,24 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
     const int ca = p.c_in * ES / 16, cb = p.c_out * ES / 16;  // 16-byte chunks per row
     const int total_a = tl.pb * ca, total_b = tl.pb * cb;
     const size_t a_row_bytes = (size_t)p.c_in * ES, b_row_bytes = (size_t)p.c_out * ES;
-    // Thread tp handles the 16-byte chunks e = tp, tp + 256, tp + 512 ... of a stage, chunk e being
-    // (row e / cpr, column chunk e % cpr).  The walk is kept as a (row, chunk) pair advanced by a
-    // constant step, so the loop has no division.
-    const int a_r0 = tp / ca, a_c0 = tp % ca, a_dr = UMMA_PROD_THREADS / ca, a_dc = UMMA_PROD_THREADS % ca;
-    const int b_r0 = tp / cb, b_c0 = tp % cb, b_dr = UMMA_PROD_THREADS / cb, b_dc = UMMA_PROD_THREADS % cb;
-
-    // gathers `total` chunks of rows idx[row] (cpr chunks each) into an MN-major operand at `sdst`
-    auto gather_rows = [&](uint32_t sdst, const uint8_t* gsrc, size_t row_bytes, const int* idx, int total, int cpr,
-                           int r0, int c0, int dr, int dc) {
-      int r = r0, c = c0;
-      for (int e = tp; e < total; e += 4 * UMMA_PROD_THREADS) {
-        int rr[4], cc[4], ix[4];
+    // Thread tp owns the 16-byte chunks e = tp, tp + 256, ... (at most 4 per operand) of every stage:
+    // chunk e is (row e / cpr, column chunk e % cpr).  Row, source column offset and shared-memory
+    // offset of each owned chunk are fixed for the whole kernel, so the stage loop has no address
+    // arithmetic beyond one multiply-add per chunk.
+    int a_row[4], b_row[4];
+    uint32_t a_dst[4], b_dst[4], a_col[4], b_col[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          rr[u] = r;
-          cc[u] = c;
-          ix[u] = (e + u * UMMA_PROD_THREADS < total) ? idx[r] : -2;
-          c += dc;
-          r += dr;
-          if (c >= cpr) { c -= cpr; ++r; }
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (ix[u] != -2) {
-            const uint32_t off = TF32 ? mnmajor32_offset((uint32_t)rr[u], (uint32_t)cc[u] * 16u, lbo, 512u)
-                                      : mnmajor_offset((uint32_t)rr[u], (uint32_t)cc[u] * 16u, lbo, 1024u);
-            const bool valid = ix[u] >= 0;
-            cp_async16(sdst + off, valid ? gsrc + ((size_t)ix[u] * row_bytes + (size_t)cc[u] * 16u) : gsrc, valid);
-          }
-        }
-      }
-    };
+    for (int u = 0; u < 4; ++u) {
+      const int e = tp + u * UMMA_PROD_THREADS;
+      a_row[u] = e < total_a ? e / ca : -1;
+      b_row[u] = e < total_b ? e / cb : -1;
+      const uint32_t ac = e < total_a ? (uint32_t)(e % ca) : 0u, bc = e < total_b ? (uint32_t)(e % cb) : 0u;
+      a_col[u] = ac * 16u;
+      b_col[u] = bc * 16u;
+      const uint32_t ar = a_row[u] < 0 ? 0u : (uint32_t)a_row[u], br = b_row[u] < 0 ? 0u : (uint32_t)b_row[u];
+      a_dst[u] = TF32 ? mnmajor32_offset(ar, ac * 16u, lbo, 512u) : mnmajor_offset(ar, ac * 16u, lbo, 1024u);
+      b_dst[u] = a_bytes + (TF32 ? mnmajor32_offset(br, bc * 16u, lbo, 512u) : mnmajor_offset(br, bc * 16u, lbo, 1024u));
+    }
 
     int issued = 0;
     for (int t = t0; t < t1 && ok; ++t) {
@@ -641,8 +627,26 @@ __global__ void __launch_bounds__(UMMA_THREADS, 1) umma_wgrad_kernel(WgradParams
       ok = warp_wait(&sh->empty[s], ((uint32_t)(issued / n_stage) & 1u) ^ 1u, abort_flag);
       if (!ok) break;
       const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
-      gather_rows(sa, feats, a_row_bytes, slot->g, total_a, ca, a_r0, a_c0, a_dr, a_dc);
-      gather_rows(sa + a_bytes, og, b_row_bytes, slot->g + UMMA_WG_MAX_PB, total_b, cb, b_r0, b_c0, b_dr, b_dc);
+      int ia[4], ib[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        ia[u] = a_row[u] >= 0 ? slot->g[a_row[u]] : -1;
+        ib[u] = b_row[u] >= 0 ? slot->g[UMMA_WG_MAX_PB + b_row[u]] : -1;
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (a_row[u] >= 0) {
+          const bool valid = ia[u] >= 0;
+          cp_async16(sa + a_dst[u], valid ? feats + ((size_t)ia[u] * a_row_bytes + a_col[u]) : feats, valid);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (b_row[u] >= 0) {
+          const bool valid = ib[u] >= 0;
+          cp_async16(sa + b_dst[u], valid ? og + ((size_t)ib[u] * b_row_bytes + b_col[u]) : og, valid);
+        }
+      }
       cp_async_arrive_noinc(smem_u32(&sh->full[s]));
       warp_arrive(&sh->gidx_empty[sl]);
       ++issued;
