@@ -9,11 +9,14 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <cstdlib>
 
 #include "common.cuh"
 #include "simt_kernels.cuh"
 #ifndef FGMS_NO_UMMA
 #include "umma_kernels.cuh"
+#include "umma_gms2.cuh"
+#include "umma_gms3.cuh"
 #endif
 
 namespace {
@@ -120,7 +123,11 @@ int run_gms(bool trans, const void* src, const void* kernel, void* dst, const in
   p.dense_rows = dense_rows; p.dense_weight = dense_weight;
 #ifndef FGMS_NO_UMMA
   if (use_umma(c_in, c_out, dtype, math)) {
-    int rc = fgms::launch_umma_gms(p, trans, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
+    static const int design = [] { const char* e = getenv("FGMS_B200_GMS_DESIGN"); return e ? atoi(e) : 3; }();
+    const bool f16 = dtype == FGMS_DTYPE_F16;
+    int rc = design == 1 ? fgms::launch_umma_gms(p, trans, f16, st, di.sms, di.max_smem_optin)
+           : design == 2 ? fgms::launch_umma_gms2(p, trans, f16, st, di.sms, di.max_smem_optin)
+                         : fgms::launch_umma_gms3(p, trans, f16, st, di.sms, di.max_smem_optin);
     if (rc == 0) return check_launch("umma_gms_kernel");
     if (rc < 0) return fail(FGMS_ERR_CUDA, "umma_gms_kernel setup failed (%d)", rc);
     // rc > 0: shape does not fit the tensor-core kernel's shared memory; take the CUDA-core path

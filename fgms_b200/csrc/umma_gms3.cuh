@@ -1,0 +1,446 @@
+// Forward / dgrad on tcgen05, warp-specialised with private hand-offs only.
+//
+//   out[scatter[j]] += src[gather[j]] . W_k        for the pairs j of every offset k
+//
+// One persistent CTA per SM walks a contiguous range of 128-pair tiles.  Seventeen warps, three roles,
+// and the only things that cross between roles are mbarrier phases:
+//
+//   producers (8 warps)  fetch their rows' map entries straight from global memory two tiles ahead,
+//                        gather feature rows with 16-byte cp.async into a ring of 16 KB stages (one
+//                        128-byte K chunk of 128 rows each, K-major SWIZZLE_128B) and, when the offset
+//                        changes, the next weight matrix into the other of two weight buffers;
+//   MMA warp             one lane issues tcgen05.mma per stage, commits the stage back to the producers
+//                        and the finished accumulator (two TMEM buffers) to the epilogue;
+//   epilogue (8 warps)   two warps per TMEM lane quarter, each owning half of every 256-byte block of the
+//                        output row: tcgen05.ld -> convert -> a 4 KB patch private to the warp -> 16-byte
+//                        vector reds with consecutive lanes on consecutive addresses of one row.  The map
+//                        entries of its 32 rows come from global memory two tiles ahead as well.
+//
+// Every role recomputes the (cheap) tile bookkeeping from the tile table in shared memory, so there is
+// no index ring and no patch hand-off.  All waits are bounded; a wait that runs out sets the CTA's
+// abort flag, every role leaves its loop, in-flight copies are awaited and TMEM is freed.
+#pragma once
+#include "common.cuh"
+#include "umma.cuh"
+
+namespace fgms {
+
+constexpr int G3_TILE_M = 128;
+constexpr int G3_EPI_WARPS = 8;
+constexpr int G3_MMA_WARP = 8;
+constexpr int G3_PROD_WARP0 = 9;
+constexpr int G3_PROD_WARPS = 8;
+constexpr int G3_PROD_THREADS = G3_PROD_WARPS * 32;
+constexpr int G3_THREADS = (G3_PROD_WARP0 + G3_PROD_WARPS) * 32;  // 544
+constexpr int G3_STAGE_BYTES = 16384;
+constexpr int G3_MAX_STAGES = 8;
+constexpr int G3_PATCH_BYTES = G3_EPI_WARPS * 4096;
+
+struct G3Shared {
+  uint64_t full[G3_MAX_STAGES];   // stage landed (one hardware arrival per producer thread)
+  uint64_t empty[G3_MAX_STAGES];  // stage consumed (tcgen05.commit)
+  uint64_t tmem_full[2];          // accumulator finished (tcgen05.commit)
+  uint64_t tmem_empty[2];         // accumulator drained (one arrival per epilogue warp)
+  uint64_t w_free[2];             // every MMA that reads this weight buffer has finished (tcgen05.commit)
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int G3_SHARED_BYTES = (sizeof(G3Shared) + 15) & ~15;
+
+struct G3Config {
+  int n_stage;  // gather stages in the ring
+  int n_wbuf;   // weight buffers: 2 when they fit, else 1 (a change of offset then drains the MMAs)
+  int w_bytes;  // k_dim * n_dim * elem
+};
+
+// one lane polls, the warp learns the outcome
+__device__ __forceinline__ bool g3_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  int ok = 1;
+  if ((threadIdx.x & 31) == 0) ok = umma::mbar_wait(umma::smem_u32(bar), parity, abort_flag) ? 1 : 0;
+  __syncwarp();  // orders the other lanes' later reads after what lane 0's acquire made visible
+  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// Walks consecutive tiles of the tile table without searching: the segment only ever moves forward.
+struct G3Walk {
+  int t, seg, seg_first, seg_end;  // tile, its segment, the segment's first tile and one past its last
+  __device__ __forceinline__ void init(const int* tile_start, int n_seg, int t_) {
+    t = t_;
+    seg = find_segment(tile_start, n_seg, t_);
+    seg_first = tile_start[seg];
+    seg_end = tile_start[seg + 1];
+  }
+  __device__ __forceinline__ void next(const int* tile_start, int n_seg) {
+    ++t;
+    while (t >= seg_end && seg + 1 < n_seg) {
+      ++seg;
+      seg_first = seg_end;
+      seg_end = tile_start[seg + 1];
+    }
+  }
+};
+struct G3Tile { int base, cnt, widx; bool dense; };
+__device__ __forceinline__ G3Tile g3_tile(const G3Walk& w, const GmsParams& p, const int* kpos_s) {
+  G3Tile ti;
+  const int lt = w.t - w.seg_first;
+  ti.dense = w.seg == p.k_vol;
+  const int seg_base = ti.dense ? 0 : kpos_s[w.seg];
+  const int seg_cnt = ti.dense ? p.dense_rows : (kpos_s[w.seg + 1] - seg_base);
+  ti.base = seg_base + lt * G3_TILE_M;
+  ti.cnt = min(G3_TILE_M, seg_cnt - lt * G3_TILE_M);
+  ti.widx = ti.dense ? p.dense_weight : w.seg;
+  return ti;
+}
+
+template <bool TF32, bool TRANS_W>
+__global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G3Config cfg) {
+  using namespace umma;
+  constexpr int ES = TF32 ? 4 : 2;
+  constexpr int EPR = 128 / ES;  // elements per 128-byte span
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  uint8_t* sW = smem;                                      // n_wbuf weight operands
+  uint8_t* sStage = sW + (size_t)cfg.n_wbuf * cfg.w_bytes;  // gather ring
+  uint8_t* sPatch = sStage + (size_t)cfg.n_stage * G3_STAGE_BYTES;
+  G3Shared* sh = reinterpret_cast<G3Shared*>(sPatch + G3_PATCH_BYTES);
+  int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + G3_SHARED_BYTES);  // [k_vol + 2]
+  int* kpos_s = tile_start + p.k_vol + 2;                                                        // [k_vol + 1]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_seg = p.k_vol + 1;
+  const int kch = p.k_dim / EPR;  // 128-byte K chunks per gathered row
+  const int n_stage = cfg.n_stage;
+  volatile int* abort_flag = &sh->abort_flag;
+
+  if (tid == 0) {
+    for (int s = 0; s < n_stage; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), G3_PROD_THREADS);
+      mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), G3_EPI_WARPS);
+      mbar_init(smem_u32(&sh->w_free[b]), 1);
+    }
+    sh->abort_flag = 0;
+    mbar_fence_init();
+  }
+  for (int s = tid; s <= p.k_vol; s += G3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
+  build_tile_table(G3_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < 2u * p.n_dim) tmem_cols <<= 1;
+  if (warp == G3_MMA_WARP) {
+    tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  int t0, t1;
+  cta_tile_range(tile_start[n_seg], &t0, &t1);
+  bool ok = true;
+  // a pair is used only if both its entries are inside the tensors
+  auto pair_ok = [&](int g, int s) { return (unsigned)g < (unsigned)p.n_gather && (unsigned)s < (unsigned)p.n_scatter; };
+
+  if (t0 >= t1) {
+    // nothing for this CTA
+  } else if (warp >= G3_PROD_WARP0) {
+    // ------------------------------------------------------------------ producers
+    // Warp pw owns tile rows [16 pw, 16 pw + 16).  Lanes 0-15 fetch those rows' gather entries, lanes
+    // 16-31 their scatter entries (needed to skip pairs whose destination is outside the tensor).
+    const int pw = warp - G3_PROD_WARP0;
+    const int tp = tid - G3_PROD_WARP0 * 32;
+    const int pc = lane & 7, rsub = lane >> 3;  // this thread copies chunk pc of rows 16 pw + rsub + 4 j
+    const uint8_t* src = static_cast<const uint8_t*>(p.src);
+    const uint8_t* wts = static_cast<const uint8_t*>(p.weights);
+    const size_t src_row_bytes = (size_t)p.k_dim * ES;
+    const uint32_t w_row_bytes = (uint32_t)p.c_out * ES;
+    uint32_t a_dst[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const uint32_t r = (uint32_t)(16 * pw + rsub + 4 * j);
+      a_dst[j] = (r >> 3) * 1024u + (r & 7u) * 128u + (((uint32_t)pc ^ (r & 7u)) << 4);
+    }
+    auto load_entry = [&](const G3Walk& w) -> int {
+      const G3Tile ti = g3_tile(w, p, kpos_s);
+      const int row = 16 * pw + (lane & 15);
+      if (row >= ti.cnt) return -1;
+      if (ti.dense) return ti.base + row;
+      return __ldg((lane < 16 ? p.gather_map : p.scatter_map) + ti.base + row);
+    };
+    auto load_weights = [&](int widx, int wb) {
+      const uint8_t* wk = wts + (size_t)widx * p.c_in * p.c_out * ES;
+      const uint32_t sw = smem_u32(sW + (size_t)wb * cfg.w_bytes);
+      if (!TRANS_W) {
+        // rows = contraction index (k_dim rows of n_dim elements): MN-major operand
+        const int cpr = p.n_dim * ES / 16, total = p.k_dim * cpr;
+        const uint32_t lbo = (uint32_t)p.k_dim * 128u;
+        for (int e = tp; e < total; e += G3_PROD_THREADS) {
+          const uint32_t row = e / cpr, c = e % cpr;
+          const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
+          cp_async16(sw + off, wk + (size_t)row * w_row_bytes + c * 16u, true);
+        }
+      } else {
+        // rows = output index (n_dim rows of k_dim elements): K-major operand
+        const int cpr = p.k_dim * ES / 16, total = p.n_dim * cpr;
+        for (int e = tp; e < total; e += G3_PROD_THREADS) {
+          const uint32_t row = e / cpr, c = e % cpr;
+          cp_async16(sw + kmajor_offset(row, c * 16u, p.n_dim), wk + (size_t)row * w_row_bytes + c * 16u, true);
+        }
+      }
+    };
+
+    G3Walk cur, pf;
+    cur.init(tile_start, n_seg, t0);
+    pf = cur;
+    int e0 = load_entry(pf), e1 = -1;
+    pf.next(tile_start, n_seg);
+    if (pf.t < t1) e1 = load_entry(pf);
+    pf.next(tile_start, n_seg);
+    int s = 0;
+    uint32_t ph = 0;          // stage and its phase
+    int cur_w = -1, n_load = -1, wb = 0;
+
+    for (int t = t0; t < t1 && ok; ++t) {
+      int e2 = -1;
+      if (pf.t < t1) e2 = load_entry(pf);
+      pf.next(tile_start, n_seg);
+      const G3Tile ti = g3_tile(cur, p, kpos_s);
+      bool new_w = false;
+      if (ti.widx != cur_w) {
+        // weight load number n_load goes to buffer n_load % n_wbuf, whose previous tenant was load
+        // n_load - n_wbuf: wait until the MMA warp has reported that tenant's last MMA finished
+        ++n_load;
+        wb = (cfg.n_wbuf == 2) ? (n_load & 1) : 0;
+        if (n_load >= cfg.n_wbuf) {
+          const uint32_t use = (uint32_t)(cfg.n_wbuf == 2 ? (n_load >> 1) : n_load) - 1u;
+          ok = g3_wait(&sh->w_free[wb], use & 1u, abort_flag);
+          if (!ok) break;
+        }
+        cur_w = ti.widx;
+        new_w = true;
+      }
+      const uint8_t* rsrc[4];
+      bool valid[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = rsub + 4 * j;
+        const int g = __shfl_sync(0xffffffffu, e0, r), sc = __shfl_sync(0xffffffffu, e0, 16 + r);
+        valid[j] = pair_ok(g, sc);
+        if (!valid[j] && pc == 0 && (g != -1 || sc != -1)) report_problem();  // entry outside the tensors: pair skipped, counted once
+        rsrc[j] = valid[j] ? src + (size_t)g * src_row_bytes + (size_t)pc * 16 : src;
+      }
+      for (int kc = 0; kc < kch && ok; ++kc) {
+        ok = g3_wait(&sh->empty[s], ph ^ 1u, abort_flag);
+        if (!ok) break;
+        if (new_w && kc == 0) load_weights(ti.widx, wb);
+        const uint32_t st = smem_u32(sStage + (size_t)s * G3_STAGE_BYTES);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) cp_async16(st + a_dst[j], rsrc[j] + (valid[j] ? (size_t)kc * 128 : 0), valid[j]);
+        // the stage's barrier hears from this thread when everything it has issued so far has landed
+        cp_async_arrive_noinc(smem_u32(&sh->full[s]));
+        if (++s == n_stage) { s = 0; ph ^= 1u; }
+      }
+      e0 = e1;
+      e1 = e2;
+      cur.next(tile_start, n_seg);
+    }
+  } else if (warp == G3_MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = make_idesc(TF32, false, !TRANS_W, G3_TILE_M, p.n_dim);
+    G3Walk cur;
+    cur.init(tile_start, n_seg, t0);
+    int s = 0;
+    uint32_t ph = 0;
+    int cur_w = -1, n_load = -1, wb = 0, tile_i = 0;
+    for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
+      const int buf = tile_i & 1;
+      const G3Tile ti = g3_tile(cur, p, kpos_s);
+      if (ti.widx != cur_w) {  // same numbering of weight loads as in the producers
+        ++n_load;
+        wb = (cfg.n_wbuf == 2) ? (n_load & 1) : 0;
+        cur_w = ti.widx;
+      }
+      cur.next(tile_start, n_seg);
+      const bool last_of_w = (t + 1 == t1) || g3_tile(cur, p, kpos_s).widx != cur_w;
+      ok = g3_wait(&sh->tmem_empty[buf], ((uint32_t)(tile_i >> 1) & 1u) ^ 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + (uint32_t)buf * p.n_dim;
+      const uint32_t sw = smem_u32(sW + (size_t)wb * cfg.w_bytes);
+      for (int kc = 0; kc < kch && ok; ++kc) {
+        ok = g3_wait(&sh->full[s], ph, abort_flag);
+        if (!ok) break;
+        if (lane == 0) {
+          fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
+          tc_fence_after();
+          const uint32_t sa = smem_u32(sStage + (size_t)s * G3_STAGE_BYTES);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) {
+            const uint64_t a_desc = make_sdesc(sa + ks * 32u, 16u, 1024u);
+            uint64_t b_desc;
+            if (!TRANS_W) {
+              // MN-major B: step (kc * EPR + ks * UMMA_K) rows of 128 bytes into the weight tile
+              const uint32_t k_row = (uint32_t)kc * EPR + (uint32_t)ks * (32u / ES);
+              b_desc = make_sdesc(sw + k_row * 128u, (uint32_t)p.k_dim * 128u, TF32 ? 512u : 1024u, TF32 ? 1u : 2u);
+            } else {
+              b_desc = make_sdesc(sw + (uint32_t)kc * ((uint32_t)p.n_dim * 128u) + ks * 32u, 16u, 1024u);
+            }
+            mma_ss<TF32>(d_tmem, a_desc, b_desc, idesc, (kc | ks) != 0);
+          }
+          mma_commit(smem_u32(&sh->empty[s]));
+          if (kc == kch - 1) {
+            mma_commit(smem_u32(&sh->tmem_full[buf]));
+            if (last_of_w) mma_commit(smem_u32(&sh->w_free[wb]));
+          }
+        }
+        __syncwarp();
+        if (++s == n_stage) { s = 0; ph ^= 1u; }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 0-7)
+    // Warp (q, h): TMEM lanes 32 q .. 32 q + 31 (a warp may only read the lane quarter given by its
+    // index mod 4) and half h of every 256-byte block of the output row.
+    const int q4 = warp & 3, hh = warp >> 2;
+    const uint32_t row_bytes = (uint32_t)p.n_dim * ES;
+    uint8_t* dst = static_cast<uint8_t*>(p.dst);
+    uint8_t* patch = sPatch + warp * 4096;  // 32 rows x 128 bytes, private to the warp
+    const uint32_t sw7 = (uint32_t)(lane & 7);
+    // destination row of tile row 32 q + lane, or -1 (beyond the tile, or an entry outside the tensors)
+    auto load_srow_parts = [&](const G3Walk& w, int* g, int* sc) {
+      const G3Tile ti = g3_tile(w, p, kpos_s);
+      const int row = 32 * q4 + lane;
+      *g = -1;
+      *sc = -1;
+      if (row < ti.cnt) {
+        if (ti.dense) { *g = ti.base + row; *sc = ti.base + row; }
+        else { *g = __ldg(p.gather_map + ti.base + row); *sc = __ldg(p.scatter_map + ti.base + row); }
+      }
+    };
+    G3Walk pf;
+    pf.init(tile_start, n_seg, t0);
+    int g0, s0, g1 = -1, s1 = -1;
+    load_srow_parts(pf, &g0, &s0);
+    pf.next(tile_start, n_seg);
+    if (pf.t < t1) load_srow_parts(pf, &g1, &s1);
+    pf.next(tile_start, n_seg);
+    int tile_i = 0;
+    for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
+      int g2 = -1, s2 = -1;
+      if (pf.t < t1) load_srow_parts(pf, &g2, &s2);
+      pf.next(tile_start, n_seg);
+      const int srow = pair_ok(g0, s0) ? s0 : -1;
+      const int buf = tile_i & 1;
+      ok = g3_wait(&sh->tmem_full[buf], (uint32_t)(tile_i >> 1) & 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * p.n_dim;
+      for (uint32_t cb = 0; cb < row_bytes; cb += 256) {
+        const uint32_t half = min(256u, row_bytes - cb) >> 1;  // bytes of this block handled by this warp: 128 or 64
+        const uint32_t my0 = cb + hh * half;
+        const uint32_t ncol = half / ES, col0 = my0 / ES;
+        for (uint32_t c0 = 0; c0 < ncol; c0 += 32) {
+          uint32_t v0[16], v1[16];
+          const bool two = c0 + 16 < ncol;
+          tmem_ld16(taddr + col0 + c0, v0);
+          if (two) tmem_ld16(taddr + col0 + c0 + 16, v1);
+          tmem_ld_wait();
+          if (TF32) {
+            const uint32_t ch0 = c0 / 4;
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + k) ^ sw7) << 4)) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
+              if (two) *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 4 + k) ^ sw7) << 4)) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
+            }
+          } else {
+            const uint32_t ch0 = c0 / 8;
+            uint32_t h[16];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+              h[k] = pack_half2(__uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
+              h[8 + k] = pack_half2(__uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
+            }
+            *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 0) ^ sw7) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+            *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 1) ^ sw7) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
+            if (two) {
+              *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 2) ^ sw7) << 4)) = make_uint4(h[8], h[9], h[10], h[11]);
+              *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 3) ^ sw7) << 4)) = make_uint4(h[12], h[13], h[14], h[15]);
+            }
+          }
+        }
+        if (cb + 256 >= row_bytes) {
+          // accumulator fully read: hand the TMEM buffer back before the reds go out
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+        }
+        __syncwarp();
+        const uint32_t cpr = half >> 4;  // 16-byte chunks per row in my part: 8 or 4
+        const uint32_t rpi = 32 / cpr;   // rows per warp-wide instruction: 4 or 8
+        const uint32_t ch = lane % cpr, rsub = lane / cpr;
+        uint8_t* dcol = dst + my0 + (ch << 4);
+#pragma unroll 4
+        for (uint32_t r0 = 0; r0 < 32; r0 += rpi) {
+          const uint32_t r = r0 + rsub;
+          const int sr = __shfl_sync(0xffffffffu, srow, r);
+          const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
+          if (sr >= 0) {
+            uint8_t* o = dcol + (size_t)sr * row_bytes;
+            if (TF32) red_add_v4(reinterpret_cast<float*>(o), __uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+            else red_add_h8(reinterpret_cast<__half*>(o), v.x, v.y, v.z, v.w);
+          }
+        }
+        __syncwarp();
+      }
+      g0 = g1; s0 = s1;
+      g1 = g2; s1 = s2;
+    }
+  }
+
+  if (!ok && lane == 0) report_problem();
+  cp_async_wait_all();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == G3_MMA_WARP) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// host launcher: 0 launched, 1 shape or pointers do not fit (caller takes the CUDA-core path), < 0 CUDA error
+template <typename K>
+inline int g3_ensure_smem(K kernel, int bytes, int slot) {
+  static int granted[4][64] = {};  // [kernel][device]: cudaFuncSetAttribute is needed once per device
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (granted[slot][dev] >= bytes) return 0;
+  if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -1;
+  granted[slot][dev] = bytes;
+  return 0;
+}
+
+inline int launch_umma_gms3(const GmsParams& p, bool trans, bool f16, cudaStream_t st, int sms, int max_smem) {
+  const int es = f16 ? 2 : 4;
+  if ((reinterpret_cast<uintptr_t>(p.src) | reinterpret_cast<uintptr_t>(p.weights) | reinterpret_cast<uintptr_t>(p.dst)) & 15) return 1;
+  G3Config cfg;
+  cfg.w_bytes = p.k_dim * p.n_dim * es;
+  const int table = ((2 * p.k_vol + 3) * 4 + 15) & ~15;
+  const int fixed = 1024 + G3_PATCH_BYTES + G3_SHARED_BYTES + table;
+  // two weight buffers if at least four gather stages still fit beside them
+  cfg.n_wbuf = (fixed + 2 * cfg.w_bytes + 4 * G3_STAGE_BYTES <= max_smem) ? 2 : 1;
+  cfg.n_stage = (max_smem - fixed - cfg.n_wbuf * cfg.w_bytes) / G3_STAGE_BYTES;
+  if (cfg.n_stage > G3_MAX_STAGES) cfg.n_stage = G3_MAX_STAGES;
+  if (cfg.n_stage < 2) return 1;
+  const int smem = fixed + cfg.n_wbuf * cfg.w_bytes + cfg.n_stage * G3_STAGE_BYTES;
+  int rc;
+  if (f16) {
+    if (trans) { rc = g3_ensure_smem(umma_gms3_kernel<false, true>, max_smem, 0); if (rc) return rc; umma_gms3_kernel<false, true><<<sms, G3_THREADS, smem, st>>>(p, cfg); }
+    else       { rc = g3_ensure_smem(umma_gms3_kernel<false, false>, max_smem, 1); if (rc) return rc; umma_gms3_kernel<false, false><<<sms, G3_THREADS, smem, st>>>(p, cfg); }
+  } else {
+    if (trans) { rc = g3_ensure_smem(umma_gms3_kernel<true, true>, max_smem, 2); if (rc) return rc; umma_gms3_kernel<true, true><<<sms, G3_THREADS, smem, st>>>(p, cfg); }
+    else       { rc = g3_ensure_smem(umma_gms3_kernel<true, false>, max_smem, 3); if (rc) return rc; umma_gms3_kernel<true, false><<<sms, G3_THREADS, smem, st>>>(p, cfg); }
+  }
+  return 0;
+}
+
+}  // namespace fgms
