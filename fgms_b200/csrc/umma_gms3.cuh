@@ -39,8 +39,8 @@ constexpr int G3_PATCH_BYTES = G3_EPI_WARPS * 4096;
 struct G3Shared {
   uint64_t full[G3_MAX_STAGES];   // stage landed (one hardware arrival per producer thread)
   uint64_t empty[G3_MAX_STAGES];  // stage consumed (tcgen05.commit)
-  uint64_t tmem_full[2];          // accumulator finished (tcgen05.commit)
-  uint64_t tmem_empty[2];         // accumulator drained (one arrival per epilogue warp)
+  uint64_t tmem_full[4];          // accumulator finished (tcgen05.commit)
+  uint64_t tmem_empty[4];         // accumulator drained (one arrival per warp of the group that owns it)
   uint64_t w_free[2];             // every MMA that reads this weight buffer has finished (tcgen05.commit)
   uint32_t tmem_base;
   int abort_flag;
@@ -51,6 +51,8 @@ struct G3Config {
   int n_stage;  // gather stages in the ring
   int n_wbuf;   // weight buffers: 2 when they fit, else 1 (a change of offset then drains the MMAs)
   int w_bytes;  // k_dim * n_dim * elem
+  int n_tbuf;   // TMEM accumulators: 4 when 4 x n_dim columns fit in the 512, else 2
+  int tbuf_shift;  // log2(n_tbuf)
 };
 
 // one lane polls, the warp learns the outcome
@@ -117,18 +119,19 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       mbar_init(smem_u32(&sh->full[s]), G3_PROD_THREADS);
       mbar_init(smem_u32(&sh->empty[s]), 1);
     }
-    for (int b = 0; b < 2; ++b) {
+    for (int b = 0; b < 4; ++b) {
       mbar_init(smem_u32(&sh->tmem_full[b]), 1);
-      mbar_init(smem_u32(&sh->tmem_empty[b]), G3_EPI_WARPS);
-      mbar_init(smem_u32(&sh->w_free[b]), 1);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), G3_EPI_WARPS / 2);
     }
+    mbar_init(smem_u32(&sh->w_free[0]), 1);
+    mbar_init(smem_u32(&sh->w_free[1]), 1);
     sh->abort_flag = 0;
     mbar_fence_init();
   }
   for (int s = tid; s <= p.k_vol; s += G3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
   build_tile_table(G3_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
   uint32_t tmem_cols = 32;
-  while (tmem_cols < 2u * p.n_dim) tmem_cols <<= 1;
+  while (tmem_cols < (uint32_t)cfg.n_tbuf * p.n_dim) tmem_cols <<= 1;
   if (warp == G3_MMA_WARP) {
     tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
     tmem_relinquish();
@@ -256,7 +259,8 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     uint32_t ph = 0;
     int cur_w = -1, n_load = -1, wb = 0, tile_i = 0;
     for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
-      const int buf = tile_i & 1;
+      const int buf = tile_i & (cfg.n_tbuf - 1);
+      const uint32_t use = (uint32_t)tile_i >> cfg.tbuf_shift;
       const G3Tile ti = g3_tile(cur, p, kpos_s);
       if (ti.widx != cur_w) {  // same numbering of weight loads as in the producers
         ++n_load;
@@ -265,7 +269,7 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       }
       cur.next(tile_start, n_seg);
       const bool last_of_w = (t + 1 == t1) || g3_tile(cur, p, kpos_s).widx != cur_w;
-      ok = g3_wait(&sh->tmem_empty[buf], ((uint32_t)(tile_i >> 1) & 1u) ^ 1u, abort_flag);
+      ok = g3_wait(&sh->tmem_empty[buf], (use & 1u) ^ 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)buf * p.n_dim;
@@ -302,15 +306,19 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0-7)
-    // Warp (q, h): TMEM lanes 32 q .. 32 q + 31 (a warp may only read the lane quarter given by its
-    // index mod 4) and half h of every 256-byte block of the output row.
-    const int q4 = warp & 3, hh = warp >> 2;
+    // Two groups of four warps take alternate tiles, so that one group's TMEM reads and conversions run
+    // while the other group's reds drain.  Warp q of a group owns TMEM lanes 32 q .. 32 q + 31 (a warp
+    // may only read the lane quarter given by its index mod 4), i.e. tile rows 32 q .. 32 q + 31, and
+    // walks the output row in 128-byte blocks: tcgen05.ld -> convert -> private patch -> reds.
+    const int grp = warp >> 2, q4 = warp & 3;
     const uint32_t row_bytes = (uint32_t)p.n_dim * ES;
+    constexpr uint32_t BLK_COLS = 128 / ES;  // accumulator columns per 128-byte block
     uint8_t* dst = static_cast<uint8_t*>(p.dst);
     uint8_t* patch = sPatch + warp * 4096;  // 32 rows x 128 bytes, private to the warp
     const uint32_t sw7 = (uint32_t)(lane & 7);
-    // destination row of tile row 32 q + lane, or -1 (beyond the tile, or an entry outside the tensors)
-    auto load_srow_parts = [&](const G3Walk& w, int* g, int* sc) {
+    const uint32_t ch = (uint32_t)(lane & 7), rsub = (uint32_t)(lane >> 3);  // red: chunk ch of rows rsub + 4 u
+    // map entries of tile row 32 q + lane (-1 beyond the tile)
+    auto load_entries = [&](const G3Walk& w, int* g, int* sc) {
       const G3Tile ti = g3_tile(w, p, kpos_s);
       const int row = 32 * q4 + lane;
       *g = -1;
@@ -320,83 +328,80 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
         else { *g = __ldg(p.gather_map + ti.base + row); *sc = __ldg(p.scatter_map + ti.base + row); }
       }
     };
-    G3Walk pf;
-    pf.init(tile_start, n_seg, t0);
-    int g0, s0, g1 = -1, s1 = -1;
-    load_srow_parts(pf, &g0, &s0);
-    pf.next(tile_start, n_seg);
-    if (pf.t < t1) load_srow_parts(pf, &g1, &s1);
-    pf.next(tile_start, n_seg);
-    int tile_i = 0;
-    for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
-      int g2 = -1, s2 = -1;
-      if (pf.t < t1) load_srow_parts(pf, &g2, &s2);
+    if (t0 + grp < t1) {
+      G3Walk pf;
+      pf.init(tile_start, n_seg, t0 + grp);
+      int g0, s0, g1 = -1, s1 = -1;
+      load_entries(pf, &g0, &s0);
       pf.next(tile_start, n_seg);
-      const int srow = pair_ok(g0, s0) ? s0 : -1;
-      const int buf = tile_i & 1;
-      ok = g3_wait(&sh->tmem_full[buf], (uint32_t)(tile_i >> 1) & 1u, abort_flag);
-      if (!ok) break;
-      tc_fence_after();
-      const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * p.n_dim;
-      for (uint32_t cb = 0; cb < row_bytes; cb += 256) {
-        const uint32_t half = min(256u, row_bytes - cb) >> 1;  // bytes of this block handled by this warp: 128 or 64
-        const uint32_t my0 = cb + hh * half;
-        const uint32_t ncol = half / ES, col0 = my0 / ES;
-        for (uint32_t c0 = 0; c0 < ncol; c0 += 32) {
-          uint32_t v0[16], v1[16];
-          const bool two = c0 + 16 < ncol;
-          tmem_ld16(taddr + col0 + c0, v0);
-          if (two) tmem_ld16(taddr + col0 + c0 + 16, v1);
-          tmem_ld_wait();
-          if (TF32) {
-            const uint32_t ch0 = c0 / 4;
+      pf.next(tile_start, n_seg);
+      if (pf.t < t1) load_entries(pf, &g1, &s1);
+      pf.next(tile_start, n_seg);
+      pf.next(tile_start, n_seg);
+      for (int t = t0 + grp; t < t1 && ok; t += 2) {
+        const int tile_i = t - t0;
+        int g2 = -1, s2 = -1;
+        if (pf.t < t1) load_entries(pf, &g2, &s2);
+        pf.next(tile_start, n_seg);
+        pf.next(tile_start, n_seg);
+        const int srow = pair_ok(g0, s0) ? s0 : -1;  // an entry outside the tensors: the pair is skipped
+        const int buf = tile_i & (cfg.n_tbuf - 1);
+        const uint32_t use = (uint32_t)tile_i >> cfg.tbuf_shift;
+        ok = g3_wait(&sh->tmem_full[buf], use & 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * p.n_dim;
+        for (uint32_t cb = 0; cb < row_bytes; cb += 128) {
+          const uint32_t col0 = cb / ES;
 #pragma unroll
-            for (int k = 0; k < 4; ++k) {
-              *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + k) ^ sw7) << 4)) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
-              if (two) *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 4 + k) ^ sw7) << 4)) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
-            }
-          } else {
-            const uint32_t ch0 = c0 / 8;
-            uint32_t h[16];
+          for (uint32_t c0 = 0; c0 < BLK_COLS; c0 += 32) {
+            uint32_t v0[16], v1[16];
+            tmem_ld16(taddr + col0 + c0, v0);
+            tmem_ld16(taddr + col0 + c0 + 16, v1);
+            tmem_ld_wait();
+            if (TF32) {
 #pragma unroll
-            for (int k = 0; k < 8; ++k) {
-              h[k] = pack_half2(__uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
-              h[8 + k] = pack_half2(__uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
-            }
-            *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 0) ^ sw7) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
-            *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 1) ^ sw7) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
-            if (two) {
-              *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 2) ^ sw7) << 4)) = make_uint4(h[8], h[9], h[10], h[11]);
-              *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + 3) ^ sw7) << 4)) = make_uint4(h[12], h[13], h[14], h[15]);
+              for (int k = 0; k < 4; ++k) {
+                *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)k ^ sw7) << 4)) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
+                *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)(4 + k) ^ sw7) << 4)) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
+              }
+            } else {
+              const uint32_t ch0 = c0 / 8;
+              uint32_t h[16];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                h[k] = pack_half2(__uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
+                h[8 + k] = pack_half2(__uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
+              }
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + k) ^ sw7) << 4)) = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
             }
           }
-        }
-        if (cb + 256 >= row_bytes) {
-          // accumulator fully read: hand the TMEM buffer back before the reds go out
-          tc_fence_before();
+          if (cb + 128 >= row_bytes) {
+            // accumulator fully read: hand the TMEM buffer back before the last reds go out
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+          }
           __syncwarp();
-          if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
-        }
-        __syncwarp();
-        const uint32_t cpr = half >> 4;  // 16-byte chunks per row in my part: 8 or 4
-        const uint32_t rpi = 32 / cpr;   // rows per warp-wide instruction: 4 or 8
-        const uint32_t ch = lane % cpr, rsub = lane / cpr;
-        uint8_t* dcol = dst + my0 + (ch << 4);
-#pragma unroll 4
-        for (uint32_t r0 = 0; r0 < 32; r0 += rpi) {
-          const uint32_t r = r0 + rsub;
-          const int sr = __shfl_sync(0xffffffffu, srow, r);
-          const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
-          if (sr >= 0) {
-            uint8_t* o = dcol + (size_t)sr * row_bytes;
-            if (TF32) red_add_v4(reinterpret_cast<float*>(o), __uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
-            else red_add_h8(reinterpret_cast<__half*>(o), v.x, v.y, v.z, v.w);
+          uint8_t* dcol = dst + cb + (ch << 4);
+#pragma unroll
+          for (uint32_t u = 0; u < 8; ++u) {
+            const uint32_t r = rsub + 4 * u;
+            const int sr = __shfl_sync(0xffffffffu, srow, r);
+            const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
+            if (sr >= 0) {
+              uint8_t* o = dcol + (size_t)sr * row_bytes;
+              if (TF32) red_add_v4(reinterpret_cast<float*>(o), __uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+              else red_add_h8(reinterpret_cast<__half*>(o), v.x, v.y, v.z, v.w);
+            }
           }
+          __syncwarp();
         }
-        __syncwarp();
+        g0 = g1; s0 = s1;
+        g1 = g2; s1 = s2;
       }
-      g0 = g1; s0 = s1;
-      g1 = g2; s1 = s2;
     }
   }
 
@@ -424,6 +429,8 @@ inline int launch_umma_gms3(const GmsParams& p, bool trans, bool f16, cudaStream
   if ((reinterpret_cast<uintptr_t>(p.src) | reinterpret_cast<uintptr_t>(p.weights) | reinterpret_cast<uintptr_t>(p.dst)) & 15) return 1;
   G3Config cfg;
   cfg.w_bytes = p.k_dim * p.n_dim * es;
+  cfg.n_tbuf = (4 * p.n_dim <= 512) ? 4 : 2;
+  cfg.tbuf_shift = cfg.n_tbuf == 4 ? 2 : 1;
   const int table = ((2 * p.k_vol + 3) * 4 + 15) & ~15;
   const int fixed = 1024 + G3_PATCH_BYTES + G3_SHARED_BYTES + table;
   // two weight buffers if at least four gather stages still fit beside them
