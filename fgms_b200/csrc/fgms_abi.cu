@@ -17,6 +17,7 @@
 #include "umma_kernels.cuh"
 #include "umma_gms2.cuh"
 #include "umma_gms3.cuh"
+#include "umma_wgrad3.cuh"
 #endif
 
 namespace {
@@ -268,7 +269,9 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   bool launched = false;
 #ifndef FGMS_NO_UMMA
   if (use_umma(c_in, c_out, dtype, math)) {
-    int rc = fgms::launch_umma_wgrad(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
+    static const int design = [] { const char* e = getenv("FGMS_B200_WGRAD_DESIGN"); return e ? atoi(e) : 3; }();
+    int rc = design == 1 ? fgms::launch_umma_wgrad(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin)
+                         : fgms::launch_umma_wgrad3(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
     if (rc == 0) {
       if (int rc2 = check_launch("umma_wgrad_kernel")) return rc2;
       launched = true;

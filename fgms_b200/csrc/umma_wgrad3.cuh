@@ -1,0 +1,373 @@
+// Weight gradient on tcgen05, warp-specialised with private hand-offs only.
+//
+//   dw[k] (c_in x c_out, fp32) += sum over the pairs j of offset k of feats[in_map[j]]^T (x) out_grad[out_map[j]]
+//
+// The pair index is the contraction index: both operands are gathered rows used MN-major.
+//   A = feats rows     [pb pairs x c_in ]   M = c_in  (tiles of 128 rows, or one tile of 64)
+//   B = out_grad rows  [pb pairs x c_out]   N = c_out
+// One persistent CTA per SM walks a contiguous range of pb-pair stages.  The accumulator stays in TMEM
+// while consecutive stages belong to the same offset and is flushed with 16-byte vector reds to the
+// fp32 gradient when the offset changes (split-K across CTAs).
+//
+//   producers (8 warps)  warp w owns rows [w pb/8, (w+1) pb/8) of every stage: it fetches those rows' map
+//                        entries from global memory four stages ahead and gathers both operands with
+//                        16-byte cp.async;
+//   MMA warp             one lane issues tcgen05.mma per stage and commits the stage back to the producers;
+//                        on a change of offset it commits the accumulator to the epilogue;
+//   epilogue (4 warps)   tcgen05.ld -> private 4 KB patch -> reds with consecutive lanes on consecutive
+//                        addresses of one gradient row.
+// All waits are bounded; a wait that runs out sets the CTA's abort flag and every role leaves its loop.
+#pragma once
+#include "common.cuh"
+#include "umma.cuh"
+#include "umma_gms3.cuh"  // G3Walk, g3_wait
+
+namespace fgms {
+
+constexpr int W3_EPI_WARPS = 4;
+constexpr int W3_MMA_WARP = 4;
+constexpr int W3_PROD_WARP0 = 5;
+constexpr int W3_PROD_WARPS = 8;
+constexpr int W3_PROD_THREADS = W3_PROD_WARPS * 32;
+constexpr int W3_THREADS = (W3_PROD_WARP0 + W3_PROD_WARPS) * 32;  // 416
+constexpr int W3_MAX_STAGES = 12;
+constexpr int W3_MAX_PB = 64;
+constexpr int W3_PATCH_BYTES = W3_EPI_WARPS * 4096;
+constexpr int W3_PREFETCH = 4;  // map entries are fetched this many stages ahead
+
+struct W3Shared {
+  uint64_t full[W3_MAX_STAGES];
+  uint64_t empty[W3_MAX_STAGES];
+  uint64_t tmem_full[4];
+  uint64_t tmem_empty[4];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+constexpr int W3_SHARED_BYTES = (sizeof(W3Shared) + 15) & ~15;
+
+struct W3Config {
+  int pb;         // pairs per stage: 16, 32 or 64
+  int n_mtile;    // 1 or 2 accumulator row tiles
+  int mtile_m;    // rows of each tile's MMA: 128 or 64
+  int alias;      // 1: the single tile has fewer real rows than mtile_m; extra rows repeat (LBO = 0)
+  int n_buf;      // TMEM accumulator sets: 1, 2 or 4
+  int buf_shift;  // log2(n_buf)
+  int n_stage;
+};
+
+// stage t of the table: first pair and number of pairs
+__device__ __forceinline__ void w3_stage(const G3Walk& w, int pb, const int* kpos_s, int* base, int* cnt) {
+  const int lt = w.t - w.seg_first;
+  const int seg_base = kpos_s[w.seg];
+  *base = seg_base + lt * pb;
+  *cnt = min(pb, kpos_s[w.seg + 1] - seg_base - lt * pb);
+}
+
+template <bool TF32>
+__global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams p, W3Config cfg) {
+  using namespace umma;
+  constexpr int ES = TF32 ? 4 : 2;
+  constexpr int UK = 32 / ES;  // contraction length of one MMA
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
+  const int pb = cfg.pb, n_stage = cfg.n_stage;
+  const uint32_t a_bytes = (uint32_t)pb * p.c_in * ES;
+  const uint32_t stage_bytes = (uint32_t)pb * (p.c_in + p.c_out) * ES;
+  uint8_t* sStage = smem;
+  uint8_t* sPatch = sStage + (size_t)n_stage * stage_bytes;
+  W3Shared* sh = reinterpret_cast<W3Shared*>(sPatch + W3_PATCH_BYTES);
+  int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + W3_SHARED_BYTES);  // [k_vol + 2]
+  int* kpos_s = tile_start + p.k_vol + 2;                                                        // [k_vol + 1]
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_seg = p.k_vol + 1;
+  volatile int* abort_flag = &sh->abort_flag;
+  const uint32_t lbo = (uint32_t)pb * 128u;  // next 128 bytes of every gathered row
+  const uint32_t buf_cols = (uint32_t)cfg.n_mtile * p.c_out;
+
+  if (tid == 0) {
+    for (int s = 0; s < n_stage; ++s) {
+      mbar_init(smem_u32(&sh->full[s]), W3_PROD_THREADS);  // one hardware arrival per producer thread
+      mbar_init(smem_u32(&sh->empty[s]), 1);
+    }
+    for (int b = 0; b < 4; ++b) {
+      mbar_init(smem_u32(&sh->tmem_full[b]), 1);
+      mbar_init(smem_u32(&sh->tmem_empty[b]), W3_EPI_WARPS);
+    }
+    sh->abort_flag = 0;
+    mbar_fence_init();
+  }
+  for (int s = tid; s <= p.k_vol; s += W3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
+  build_tile_table(pb, p.kpos, p.k_vol, 0, tile_start);  // syncs the CTA
+  uint32_t tmem_cols = 32;
+  while (tmem_cols < buf_cols * (uint32_t)cfg.n_buf) tmem_cols <<= 1;
+  if (warp == W3_MMA_WARP) {
+    tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh->tmem_base;
+
+  int t0, t1;
+  cta_tile_range(tile_start[n_seg], &t0, &t1);
+  bool ok = true;
+
+  if (t0 >= t1) {
+    // nothing for this CTA
+  } else if (warp >= W3_PROD_WARP0) {
+    // ------------------------------------------------------------------ producers
+    const int pw = warp - W3_PROD_WARP0;
+    const int rpw = pb >> 3;  // rows of a stage owned by this warp: 2, 4 or 8
+    const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
+    const uint8_t* og = static_cast<const uint8_t*>(p.out_grad);
+    const int ca = p.c_in * ES / 16, cb = p.c_out * ES / 16;  // 16-byte chunks per row
+    const int total_a = rpw * ca, total_b = rpw * cb;         // chunks of this warp per stage and operand (<= 128)
+    const size_t a_row_bytes = (size_t)p.c_in * ES, b_row_bytes = (size_t)p.c_out * ES;
+    // Thread `lane` owns the chunks e = lane, lane + 32, ... (at most 4 per operand) of the warp's rows:
+    // chunk e is (row e / cpr, column chunk e % cpr).  Everything about a chunk except the row's map
+    // entry is fixed for the whole kernel.
+    int a_rl[4], b_rl[4];  // lane that holds the row's map entry (-1: no such chunk)
+    uint32_t a_dst[4], b_dst[4], a_col[4], b_col[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int e = lane + 32 * u;
+      const bool ha = e < total_a, hb = e < total_b;
+      const uint32_t ar = ha ? (uint32_t)(e / ca) : 0u, br = hb ? (uint32_t)(e / cb) : 0u;
+      const uint32_t ac = ha ? (uint32_t)(e % ca) : 0u, bc = hb ? (uint32_t)(e % cb) : 0u;
+      a_rl[u] = ha ? (int)ar : -1;
+      b_rl[u] = hb ? 8 + (int)br : -1;
+      a_col[u] = ac * 16u;
+      b_col[u] = bc * 16u;
+      const uint32_t arow = (uint32_t)(pw * rpw) + ar, brow = (uint32_t)(pw * rpw) + br;
+      a_dst[u] = TF32 ? mnmajor32_offset(arow, ac * 16u, lbo, 512u) : mnmajor_offset(arow, ac * 16u, lbo, 1024u);
+      b_dst[u] = a_bytes + (TF32 ? mnmajor32_offset(brow, bc * 16u, lbo, 512u) : mnmajor_offset(brow, bc * 16u, lbo, 1024u));
+    }
+    // lanes 0..7 fetch in_map of the warp's rows, lanes 8..15 out_map (-1 beyond the stage)
+    auto load_entry = [&](const G3Walk& w) -> int {
+      int base, cnt;
+      w3_stage(w, pb, kpos_s, &base, &cnt);
+      const int r = lane & 7;
+      const int row = pw * rpw + r;
+      if (lane >= 16 || r >= rpw || row >= cnt) return -1;
+      return __ldg((lane < 8 ? p.in_map : p.out_map) + base + row);
+    };
+    G3Walk pf;
+    pf.init(tile_start, n_seg, t0);
+    int e[W3_PREFETCH];
+#pragma unroll
+    for (int d = 0; d < W3_PREFETCH; ++d) {
+      e[d] = (pf.t < t1) ? load_entry(pf) : -1;
+      pf.next(tile_start, n_seg);
+    }
+    int s = 0;
+    uint32_t ph = 0;
+    for (int t = t0; t < t1 && ok; ++t) {
+      int cur = e[0];
+#pragma unroll
+      for (int d = 0; d + 1 < W3_PREFETCH; ++d) e[d] = e[d + 1];
+      e[W3_PREFETCH - 1] = (pf.t < t1) ? load_entry(pf) : -1;
+      pf.next(tile_start, n_seg);
+      // a pair is used only if both its entries are inside the tensors
+      {
+        const int other = __shfl_xor_sync(0xffffffffu, cur, 8);
+        const int a = lane < 8 ? cur : other, b = lane < 8 ? other : cur;
+        const bool okp = (unsigned)a < (unsigned)p.n_in && (unsigned)b < (unsigned)p.n_out;
+        if (!okp) {
+          if (lane < 8 && (a != -1 || b != -1)) report_problem();  // counted once per skipped pair
+          cur = -1;
+        }
+      }
+      ok = g3_wait(&sh->empty[s], ph ^ 1u, abort_flag);
+      if (!ok) break;
+      const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int ia = __shfl_sync(0xffffffffu, cur, a_rl[u] & 31);
+        if (a_rl[u] >= 0) {
+          const bool valid = ia >= 0;
+          cp_async16(sa + a_dst[u], valid ? feats + ((size_t)ia * a_row_bytes + a_col[u]) : feats, valid);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int ib = __shfl_sync(0xffffffffu, cur, b_rl[u] & 31);
+        if (b_rl[u] >= 0) {
+          const bool valid = ib >= 0;
+          cp_async16(sa + b_dst[u], valid ? og + ((size_t)ib * b_row_bytes + b_col[u]) : og, valid);
+        }
+      }
+      // the stage's barrier hears from this thread when everything it has issued so far has landed
+      cp_async_arrive_noinc(smem_u32(&sh->full[s]));
+      if (++s == n_stage) { s = 0; ph ^= 1u; }
+    }
+  } else if (warp == W3_MMA_WARP) {
+    // ------------------------------------------------------------------ MMA issuer
+    const uint32_t idesc = make_idesc(TF32, true, true, cfg.mtile_m, p.c_out);
+    const uint32_t sbo = TF32 ? 512u : 1024u, ltype = TF32 ? 1u : 2u;
+    const uint32_t a_lbo = cfg.alias ? 0u : lbo;
+    const uint32_t mtile_stride = (uint32_t)(cfg.mtile_m * ES / 128) * lbo;  // A start of the second row tile
+    G3Walk cur;
+    cur.init(tile_start, n_seg, t0);
+    int s = 0, run_i = 0, cur_seg = -1;
+    uint32_t ph = 0;
+    bool first = true;
+    for (int t = t0; t < t1 && ok; ++t) {
+      if (cur.seg != cur_seg) {
+        if (cur_seg >= 0) {
+          if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[run_i & (cfg.n_buf - 1)]));
+          __syncwarp();
+          ++run_i;
+        }
+        cur_seg = cur.seg;
+        first = true;
+        const uint32_t use = (uint32_t)run_i >> cfg.buf_shift;
+        ok = g3_wait(&sh->tmem_empty[run_i & (cfg.n_buf - 1)], (use & 1u) ^ 1u, abort_flag);
+        if (!ok) break;
+        tc_fence_after();
+      }
+      const int buf = run_i & (cfg.n_buf - 1);
+      ok = g3_wait(&sh->full[s], ph, abort_flag);
+      if (!ok) break;
+      if (lane == 0) {
+        fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
+        tc_fence_after();
+        const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
+        const uint32_t sb = sa + a_bytes;
+        for (int ks = 0; ks < pb / UK; ++ks) {
+          const uint32_t kadv = (uint32_t)ks * UK * 128u;
+          const uint64_t b_desc = make_sdesc(sb + kadv, lbo, sbo, ltype);
+          for (int mt = 0; mt < cfg.n_mtile; ++mt) {
+            const uint64_t a_desc = make_sdesc(sa + kadv + mt * mtile_stride, a_lbo, sbo, ltype);
+            mma_ss<TF32>(tmem_base + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out, a_desc, b_desc, idesc,
+                         !(first && ks == 0));
+          }
+        }
+        mma_commit(smem_u32(&sh->empty[s]));
+      }
+      __syncwarp();
+      first = false;
+      if (++s == n_stage) { s = 0; ph ^= 1u; }
+      cur.next(tile_start, n_seg);
+    }
+    if (ok && cur_seg >= 0) {
+      if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[run_i & (cfg.n_buf - 1)]));
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue (warps 0-3)
+    // Thread (warp, lane) holds accumulator row m in its TMEM lane.  32 columns of the warp's 32 rows
+    // go through the warp's patch so that eight consecutive lanes add 128 consecutive bytes of one row.
+    uint8_t* patch = sPatch + warp * 4096;
+    const uint32_t sw7 = (uint32_t)(lane & 7);
+    const uint32_t ch = (uint32_t)(lane & 7), rsub = (uint32_t)(lane >> 3);
+    int run_i = 0;
+    int t = t0;
+    while (t < t1 && ok) {
+      const int seg = find_segment(tile_start, n_seg, t);
+      t = min(t1, tile_start[seg + 1]);  // this CTA's stages of the offset end here
+      const int buf = run_i & (cfg.n_buf - 1);
+      const uint32_t use = (uint32_t)run_i >> cfg.buf_shift;
+      ok = g3_wait(&sh->tmem_full[buf], use & 1u, abort_flag);
+      if (!ok) break;
+      tc_fence_after();
+      float* dwk = p.dw + (size_t)seg * p.c_in * p.c_out;
+      for (int mt = 0; mt < cfg.n_mtile; ++mt) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out;
+        for (int c0 = 0; c0 < p.c_out; c0 += 32) {
+          uint32_t v0[16], v1[16];
+          tmem_ld16(taddr + c0, v0);
+          tmem_ld16(taddr + c0 + 16, v1);
+          tmem_ld_wait();
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)k ^ sw7) << 4)) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
+            *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)(4 + k) ^ sw7) << 4)) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
+          }
+          __syncwarp();
+#pragma unroll
+          for (uint32_t u = 0; u < 8; ++u) {
+            const uint32_t r = rsub + 4 * u;  // TMEM lane (within the warp's quarter) whose row this is
+            // M = 128: lane r of warp w is row 32 w + r; M = 64: row i lives in lane (i / 16) * 32 + i % 16
+            int m;
+            if (cfg.mtile_m == 128) m = mt * 128 + warp * 32 + (int)r;
+            else m = r < 16 ? warp * 16 + (int)r : -1;
+            const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
+            if (m >= 0 && m < p.c_in)
+              red_add_v4(dwk + (size_t)m * p.c_out + c0 + (ch << 2), __uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
+          }
+          __syncwarp();
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh->tmem_empty[buf]));
+      ++run_i;
+    }
+  }
+
+  if (!ok && lane == 0) report_problem();
+  cp_async_wait_all();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == W3_MMA_WARP) tmem_dealloc(tmem_base, tmem_cols);
+}
+
+// Accumulator row tiling for c_in: whole 128-row tiles, a single 64-row tile, or a single tile whose
+// rows beyond c_in repeat the real ones.  Returns false for shapes that are not covered (e.g. 192 rows).
+inline bool w3_config(int c_in, int c_out, int es, int max_smem, int k_vol, W3Config* cfg) {
+  const int span = 128 / es;  // rows per 128-byte span of a gathered feature row
+  if (c_in % 128 == 0) { cfg->n_mtile = c_in / 128; cfg->mtile_m = 128; cfg->alias = 0; }
+  else if (c_in == 64) { cfg->n_mtile = 1; cfg->mtile_m = 64; cfg->alias = 0; }
+  else if (c_in == span) { cfg->n_mtile = 1; cfg->mtile_m = 64; cfg->alias = 1; }  // tf32, 32 rows
+  else return false;
+  if (cfg->n_mtile > 2) return false;
+  const int buf_cols = cfg->n_mtile * c_out;
+  if (buf_cols > 512) return false;
+  cfg->n_buf = 4 * buf_cols <= 512 ? 4 : (2 * buf_cols <= 512 ? 2 : 1);
+  cfg->buf_shift = cfg->n_buf == 4 ? 2 : (cfg->n_buf == 2 ? 1 : 0);
+  // pairs per stage: a producer thread holds at most 4 chunks per operand (pb/8 rows x chunks per row <= 128)
+  const int cmax = (c_in > c_out ? c_in : c_out) * es / 16;
+  int pb = W3_MAX_PB;
+  while (pb > 16 && (pb / 8) * cmax > 128) pb >>= 1;
+  if ((pb / 8) * cmax > 128) return false;
+  const int fixed = 1024 + W3_PATCH_BYTES + W3_SHARED_BYTES + (((2 * k_vol + 3) * 4 + 15) & ~15);
+  const int row_bytes = (c_in + c_out) * es;
+  while (pb > 16 && (max_smem - fixed) / (pb * row_bytes) < 4) pb >>= 1;  // keep at least four stages in flight
+  int n_stage = (max_smem - fixed) / (pb * row_bytes);
+  if (n_stage > W3_MAX_STAGES) n_stage = W3_MAX_STAGES;
+  if (n_stage < 2) return false;
+  cfg->pb = pb;
+  cfg->n_stage = n_stage;
+  return true;
+}
+
+// host launcher: 0 launched, 1 shape or pointers do not fit (caller takes the CUDA-core path), < 0 CUDA error
+inline int launch_umma_wgrad3(const WgradParams& p, bool f16, cudaStream_t st, int sms, int max_smem) {
+  const int es = f16 ? 2 : 4;
+  if ((reinterpret_cast<uintptr_t>(p.feats) | reinterpret_cast<uintptr_t>(p.out_grad) | reinterpret_cast<uintptr_t>(p.dw)) & 15) return 1;
+  W3Config cfg;
+  if (!w3_config(p.c_in, p.c_out, es, max_smem, p.k_vol, &cfg)) return 1;
+  const int smem = 1024 + W3_PATCH_BYTES + W3_SHARED_BYTES + (((2 * p.k_vol + 3) * 4 + 15) & ~15) +
+                   cfg.n_stage * cfg.pb * (p.c_in + p.c_out) * es;
+  static int granted[2][64] = {};  // cudaFuncSetAttribute is needed once per device and kernel
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
+  if (f16) {
+    if (granted[0][dev] < max_smem) {
+      if (cudaFuncSetAttribute(umma_wgrad3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) return -1;
+      granted[0][dev] = max_smem;
+    }
+    umma_wgrad3_kernel<false><<<sms, W3_THREADS, smem, st>>>(p, cfg);
+  } else {
+    if (granted[1][dev] < max_smem) {
+      if (cudaFuncSetAttribute(umma_wgrad3_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) return -1;
+      granted[1][dev] = max_smem;
+    }
+    umma_wgrad3_kernel<true><<<sms, W3_THREADS, smem, st>>>(p, cfg);
+  }
+  return 0;
+}
+
+}  // namespace fgms
