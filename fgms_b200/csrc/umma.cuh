@@ -61,6 +61,10 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
   const uint32_t n = valid ? 16u : 0u;
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
+// same with the number of bytes to read (16, or 0 for a zero-filled chunk) already in a register
+__device__ __forceinline__ void cp_async16_n(uint32_t dst, const void* src, uint32_t n) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

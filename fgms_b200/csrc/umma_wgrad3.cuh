@@ -27,17 +27,21 @@ namespace fgms {
 constexpr int W3_EPI_WARPS = 4;
 constexpr int W3_MMA_WARP = 4;
 constexpr int W3_PROD_WARP0 = 5;
-constexpr int W3_PROD_WARPS = 8;
+#ifndef W3_PROD_WARPS_N
+#define W3_PROD_WARPS_N 8
+#endif
+constexpr int W3_PROD_WARPS = W3_PROD_WARPS_N;  // 8 or 16
 constexpr int W3_PROD_THREADS = W3_PROD_WARPS * 32;
-constexpr int W3_THREADS = (W3_PROD_WARP0 + W3_PROD_WARPS) * 32;  // 416
+constexpr int W3_THREADS = (W3_PROD_WARP0 + W3_PROD_WARPS) * 32;
+__device__ __forceinline__ int w3_producer_index(int warp) { return warp - W3_PROD_WARP0; }  // < 0: no producer
 constexpr int W3_MAX_STAGES = 12;
-constexpr int W3_MAX_PB = 64;
+constexpr int W3_MAX_PB = 128;
 constexpr int W3_PATCH_BYTES = W3_EPI_WARPS * 4096;
 constexpr int W3_PREFETCH = 4;  // map entries are fetched this many stages ahead
 
 struct W3Shared {
   uint64_t full[W3_MAX_STAGES];
-  uint64_t empty[W3_MAX_STAGES];
+  uint64_t empty[W3_MAX_STAGES];  // used at the first stage of every group: the group's stages have been consumed
   uint64_t tmem_full[4];
   uint64_t tmem_empty[4];
   uint32_t tmem_base;
@@ -46,13 +50,14 @@ struct W3Shared {
 constexpr int W3_SHARED_BYTES = (sizeof(W3Shared) + 15) & ~15;
 
 struct W3Config {
-  int pb;         // pairs per stage: 16, 32 or 64
+  int pb;         // pairs per stage: 32, 64 or 128
   int n_mtile;    // 1 or 2 accumulator row tiles
   int mtile_m;    // rows of each tile's MMA: 128 or 64
   int alias;      // 1: the single tile has fewer real rows than mtile_m; extra rows repeat (LBO = 0)
   int n_buf;      // TMEM accumulator sets: 1, 2 or 4
   int buf_shift;  // log2(n_buf)
-  int n_stage;
+  int n_stage;    // a multiple of `group`
+  int group;      // stages handed back to the producers by one tcgen05.commit (a commit drains the MMA pipe)
 };
 
 // stage t of the table: first pair and number of pairs
@@ -116,42 +121,35 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
 
   if (t0 >= t1) {
     // nothing for this CTA
-  } else if (warp >= W3_PROD_WARP0) {
+  } else if (w3_producer_index(warp) >= 0) {
     // ------------------------------------------------------------------ producers
-    const int pw = warp - W3_PROD_WARP0;
-    const int rpw = pb >> 3;  // rows of a stage owned by this warp: 2, 4 or 8
+    const int pw = w3_producer_index(warp);
+    const int rpw = pb / W3_PROD_WARPS;  // rows of a stage owned by this warp: 4, 8 or 16
+    const int n_pass = rpw >> 2;         // a warp-wide copy covers 4 rows x 128 bytes
     const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
     const uint8_t* og = static_cast<const uint8_t*>(p.out_grad);
-    const int ca = p.c_in * ES / 16, cb = p.c_out * ES / 16;  // 16-byte chunks per row
-    const int total_a = rpw * ca, total_b = rpw * cb;         // chunks of this warp per stage and operand (<= 128)
-    const size_t a_row_bytes = (size_t)p.c_in * ES, b_row_bytes = (size_t)p.c_out * ES;
-    // Thread `lane` owns the chunks e = lane, lane + 32, ... (at most 4 per operand) of the warp's rows:
-    // chunk e is (row e / cpr, column chunk e % cpr).  Everything about a chunk except the row's map
-    // entry is fixed for the whole kernel.
-    int a_rl[4], b_rl[4];  // lane that holds the row's map entry (-1: no such chunk)
-    uint32_t a_dst[4], b_dst[4], a_col[4], b_col[4];
+    const int nha = p.c_in * ES / 128, nhb = p.c_out * ES / 128;  // 128-byte pieces per row: 1 .. 8
+    const uint32_t a_row_bytes = (uint32_t)p.c_in * ES, b_row_bytes = (uint32_t)p.c_out * ES;
+    // Lane (rs, c) = (lane / 8, lane % 8) copies 16-byte chunk c of every 128-byte piece of the rows
+    // rs, rs + 4, ... of the warp's block: one shuffle and one address per row, then one cp.async per
+    // piece at a fixed distance (128 bytes in global memory, `lbo` in shared memory).
+    const int rs = lane >> 3, cc = lane & 7;
+    uint32_t dst_rel[4];  // piece 0 of row rs + 4 u, relative to the operand's start in the stage
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int e = lane + 32 * u;
-      const bool ha = e < total_a, hb = e < total_b;
-      const uint32_t ar = ha ? (uint32_t)(e / ca) : 0u, br = hb ? (uint32_t)(e / cb) : 0u;
-      const uint32_t ac = ha ? (uint32_t)(e % ca) : 0u, bc = hb ? (uint32_t)(e % cb) : 0u;
-      a_rl[u] = ha ? (int)ar : -1;
-      b_rl[u] = hb ? 8 + (int)br : -1;
-      a_col[u] = ac * 16u;
-      b_col[u] = bc * 16u;
-      const uint32_t arow = (uint32_t)(pw * rpw) + ar, brow = (uint32_t)(pw * rpw) + br;
-      a_dst[u] = TF32 ? mnmajor32_offset(arow, ac * 16u, lbo, 512u) : mnmajor_offset(arow, ac * 16u, lbo, 1024u);
-      b_dst[u] = a_bytes + (TF32 ? mnmajor32_offset(brow, bc * 16u, lbo, 512u) : mnmajor_offset(brow, bc * 16u, lbo, 1024u));
+      const uint32_t row = (uint32_t)(pw * rpw + rs + 4 * u);
+      dst_rel[u] = TF32 ? mnmajor32_offset(row, (uint32_t)cc * 16u, lbo, 512u) : mnmajor_offset(row, (uint32_t)cc * 16u, lbo, 1024u);
     }
-    // lanes 0..7 fetch in_map of the warp's rows, lanes 8..15 out_map (-1 beyond the stage)
+    const uint8_t* feats_c = feats + cc * 16;
+    const uint8_t* og_c = og + cc * 16;
+    // lanes 0..15 fetch in_map of the warp's rows, lanes 16..31 out_map (-1 beyond the stage)
     auto load_entry = [&](const G3Walk& w) -> int {
       int base, cnt;
       w3_stage(w, pb, kpos_s, &base, &cnt);
-      const int r = lane & 7;
+      const int r = lane & 15;
       const int row = pw * rpw + r;
-      if (lane >= 16 || r >= rpw || row >= cnt) return -1;
-      return __ldg((lane < 8 ? p.in_map : p.out_map) + base + row);
+      if (r >= rpw || row >= cnt) return -1;
+      return __ldg((lane < 16 ? p.in_map : p.out_map) + base + row);
     };
     G3Walk pf;
     pf.init(tile_start, n_seg, t0);
@@ -161,7 +159,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
       e[d] = (pf.t < t1) ? load_entry(pf) : -1;
       pf.next(tile_start, n_seg);
     }
-    int s = 0;
+    int s = 0, sg = 0;  // stage, and its position in its group
     uint32_t ph = 0;
     for (int t = t0; t < t1 && ok; ++t) {
       int cur = e[0];
@@ -171,35 +169,40 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
       pf.next(tile_start, n_seg);
       // a pair is used only if both its entries are inside the tensors
       {
-        const int other = __shfl_xor_sync(0xffffffffu, cur, 8);
-        const int a = lane < 8 ? cur : other, b = lane < 8 ? other : cur;
+        const int other = __shfl_xor_sync(0xffffffffu, cur, 16);
+        const int a = lane < 16 ? cur : other, b = lane < 16 ? other : cur;
         const bool okp = (unsigned)a < (unsigned)p.n_in && (unsigned)b < (unsigned)p.n_out;
         if (!okp) {
-          if (lane < 8 && (a != -1 || b != -1)) report_problem();  // counted once per skipped pair
+          if (lane < 16 && (a != -1 || b != -1)) report_problem();  // counted once per skipped pair
           cur = -1;
         }
       }
-      ok = g3_wait(&sh->empty[s], ph ^ 1u, abort_flag);
-      if (!ok) break;
-      const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int ia = __shfl_sync(0xffffffffu, cur, a_rl[u] & 31);
-        if (a_rl[u] >= 0) {
-          const bool valid = ia >= 0;
-          cp_async16(sa + a_dst[u], valid ? feats + ((size_t)ia * a_row_bytes + a_col[u]) : feats, valid);
-        }
+      if (sg == 0) {
+        ok = g3_wait(&sh->empty[s], ph ^ 1u, abort_flag);
+        if (!ok) break;
       }
+      const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
+      const uint32_t sb = sa + a_bytes;
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int ib = __shfl_sync(0xffffffffu, cur, b_rl[u] & 31);
-        if (b_rl[u] >= 0) {
-          const bool valid = ib >= 0;
-          cp_async16(sa + b_dst[u], valid ? og + ((size_t)ib * b_row_bytes + b_col[u]) : og, valid);
+        if (u < n_pass) {
+          const int ia = __shfl_sync(0xffffffffu, cur, rs + 4 * u);
+          const int ib = __shfl_sync(0xffffffffu, cur, 16 + rs + 4 * u);
+          const uint32_t na = ia >= 0 ? 16u : 0u, nb = ib >= 0 ? 16u : 0u;  // 0 bytes read: the chunk is zero-filled
+          const uint8_t* pa = feats_c + (size_t)max(ia, 0) * a_row_bytes;
+          const uint8_t* pb_ = og_c + (size_t)max(ib, 0) * b_row_bytes;
+          const uint32_t da = sa + dst_rel[u], db = sb + dst_rel[u];
+#pragma unroll
+          for (int h = 0; h < 8; ++h)
+            if (h < nha) cp_async16_n(da + (uint32_t)h * lbo, pa + h * 128, na);
+#pragma unroll
+          for (int h = 0; h < 8; ++h)
+            if (h < nhb) cp_async16_n(db + (uint32_t)h * lbo, pb_ + h * 128, nb);
         }
       }
       // the stage's barrier hears from this thread when everything it has issued so far has landed
       cp_async_arrive_noinc(smem_u32(&sh->full[s]));
+      if (++sg == cfg.group) sg = 0;
       if (++s == n_stage) { s = 0; ph ^= 1u; }
     }
   } else if (warp == W3_MMA_WARP) {
@@ -210,7 +213,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     const uint32_t mtile_stride = (uint32_t)(cfg.mtile_m * ES / 128) * lbo;  // A start of the second row tile
     G3Walk cur;
     cur.init(tile_start, n_seg, t0);
-    int s = 0, run_i = 0, cur_seg = -1;
+    int s = 0, sg = 0, run_i = 0, cur_seg = -1;
     uint32_t ph = 0;
     bool first = true;
     for (int t = t0; t < t1 && ok; ++t) {
@@ -244,10 +247,12 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
                          !(first && ks == 0));
           }
         }
-        mma_commit(smem_u32(&sh->empty[s]));
+        // one commit per group of stages (and one for the CTA's last stage, which nobody waits for)
+        if (sg == cfg.group - 1 || t + 1 == t1) mma_commit(smem_u32(&sh->empty[s - sg]));
       }
       __syncwarp();
       first = false;
+      if (++sg == cfg.group) sg = 0;
       if (++s == n_stage) { s = 0; ph ^= 1u; }
       cur.next(tile_start, n_seg);
     }
@@ -255,7 +260,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
       if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[run_i & (cfg.n_buf - 1)]));
       __syncwarp();
     }
-  } else {
+  } else if (warp < W3_EPI_WARPS) {
     // ------------------------------------------------------------------ epilogue (warps 0-3)
     // Thread (warp, lane) holds accumulator row m in its TMEM lane.  32 columns of the warp's 32 rows
     // go through the warp's patch so that eight consecutive lanes add 128 consecutive bytes of one row.
@@ -316,7 +321,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
 
 // Accumulator row tiling for c_in: whole 128-row tiles, a single 64-row tile, or a single tile whose
 // rows beyond c_in repeat the real ones.  Returns false for shapes that are not covered (e.g. 192 rows).
-inline bool w3_config(int c_in, int c_out, int es, int max_smem, int k_vol, W3Config* cfg) {
+inline bool w3_config(int c_in, int c_out, int es, int max_smem, int k_vol, int pb_cap, W3Config* cfg) {
   const int span = 128 / es;  // rows per 128-byte span of a gathered feature row
   if (c_in % 128 == 0) { cfg->n_mtile = c_in / 128; cfg->mtile_m = 128; cfg->alias = 0; }
   else if (c_in == 64) { cfg->n_mtile = 1; cfg->mtile_m = 64; cfg->alias = 0; }
@@ -327,17 +332,18 @@ inline bool w3_config(int c_in, int c_out, int es, int max_smem, int k_vol, W3Co
   if (buf_cols > 512) return false;
   cfg->n_buf = 4 * buf_cols <= 512 ? 4 : (2 * buf_cols <= 512 ? 2 : 1);
   cfg->buf_shift = cfg->n_buf == 4 ? 2 : (cfg->n_buf == 2 ? 1 : 0);
-  // pairs per stage: a producer thread holds at most 4 chunks per operand (pb/8 rows x chunks per row <= 128)
-  const int cmax = (c_in > c_out ? c_in : c_out) * es / 16;
-  int pb = W3_MAX_PB;
-  while (pb > 16 && (pb / 8) * cmax > 128) pb >>= 1;
-  if ((pb / 8) * cmax > 128) return false;
+  // pairs per stage: 4, 8 or 16 rows per producer warp
+  int pb = pb_cap;
   const int fixed = 1024 + W3_PATCH_BYTES + W3_SHARED_BYTES + (((2 * k_vol + 3) * 4 + 15) & ~15);
   const int row_bytes = (c_in + c_out) * es;
-  while (pb > 16 && (max_smem - fixed) / (pb * row_bytes) < 4) pb >>= 1;  // keep at least four stages in flight
+  while (pb > 32 && (max_smem - fixed) / (pb * row_bytes) < 3) pb >>= 1;  // keep at least three stages in flight
   int n_stage = (max_smem - fixed) / (pb * row_bytes);
   if (n_stage > W3_MAX_STAGES) n_stage = W3_MAX_STAGES;
   if (n_stage < 2) return false;
+  // stages per commit: as many as leave three groups in flight
+  cfg->group = 1;
+  for (int g = 4; g >= 2; --g)
+    if ((n_stage - n_stage % g) / g >= 3) { cfg->group = g; n_stage -= n_stage % g; break; }
   cfg->pb = pb;
   cfg->n_stage = n_stage;
   return true;
@@ -348,7 +354,8 @@ inline int launch_umma_wgrad3(const WgradParams& p, bool f16, cudaStream_t st, i
   const int es = f16 ? 2 : 4;
   if ((reinterpret_cast<uintptr_t>(p.feats) | reinterpret_cast<uintptr_t>(p.out_grad) | reinterpret_cast<uintptr_t>(p.dw)) & 15) return 1;
   W3Config cfg;
-  if (!w3_config(p.c_in, p.c_out, es, max_smem, p.k_vol, &cfg)) return 1;
+  static const int pb_cap = [] { const char* e = getenv("FGMS_B200_WGRAD_PB"); const int v = e ? atoi(e) : W3_MAX_PB; return (v == 32 || v == 64 || v == 128) ? v : W3_MAX_PB; }();
+  if (!w3_config(p.c_in, p.c_out, es, max_smem, p.k_vol, pb_cap, &cfg)) return 1;
   const int smem = 1024 + W3_PATCH_BYTES + W3_SHARED_BYTES + (((2 * p.k_vol + 3) * 4 + 15) & ~15) +
                    cfg.n_stage * cfg.pb * (p.c_in + p.c_out) * es;
   static int granted[2][64] = {};  // cudaFuncSetAttribute is needed once per device and kernel
