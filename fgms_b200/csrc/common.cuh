@@ -52,20 +52,28 @@ struct WgradParams {
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ void build_tile_table(int TILE, const int32_t* __restrict__ kpos, int k_vol,
                                                  int dense_rows, int* tile_start /* [k_vol+2] */) {
-  // counts first (parallel), then one thread does the short prefix sum
+  // counts first (parallel), then the first warp turns them into running sums, 32 segments at a time
   for (int s = threadIdx.x; s <= k_vol; s += blockDim.x) {
     int cnt = (s < k_vol) ? (__ldg(kpos + s + 1) - __ldg(kpos + s)) : dense_rows;
     if (cnt < 0) cnt = 0;
     tile_start[s + 1] = (cnt + TILE - 1) / TILE;
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    tile_start[0] = 0;
-    int run = 0;
-    for (int s = 0; s <= k_vol; ++s) {
-      run += tile_start[s + 1];
-      tile_start[s + 1] = run;
+  if (threadIdx.x < 32) {
+    const int lane = threadIdx.x;
+    int carry = 0;
+    for (int s0 = 0; s0 <= k_vol; s0 += 32) {
+      const int s = s0 + lane;
+      int v = s <= k_vol ? tile_start[s + 1] : 0;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int n = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += n;
+      }
+      if (s <= k_vol) tile_start[s + 1] = v + carry;
+      carry += __shfl_sync(0xffffffffu, v, 31);
     }
+    if (lane == 0) tile_start[0] = 0;
   }
   __syncthreads();
 }

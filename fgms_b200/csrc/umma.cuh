@@ -65,6 +65,16 @@ __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool v
 __device__ __forceinline__ void cp_async16_n(uint32_t dst, const void* src, uint32_t n) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(n) : "memory");
 }
+// 4-byte copy (goes through L1): used to prefetch map entries into shared memory without tying up a register
+__device__ __forceinline__ void cp_async4(uint32_t dst, const void* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void st_shared_i32(uint32_t dst, int v) { asm volatile("st.shared.b32 [%0], %1;" ::"r"(dst), "r"(v) : "memory"); }
+__device__ __forceinline__ int ld_shared_i32(uint32_t src) {
+  int v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(src) : "memory");
+  return v;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() {

@@ -35,6 +35,11 @@ constexpr int G3_THREADS = (G3_PROD_WARP0 + G3_PROD_WARPS) * 32;  // 544
 constexpr int G3_STAGE_BYTES = 16384;
 constexpr int G3_MAX_STAGES = 8;
 constexpr int G3_PATCH_BYTES = G3_EPI_WARPS * 4096;
+// Map entries are prefetched two tiles ahead with 4-byte cp.async into a ring private to each warp (each
+// lane writes and later reads only its own word, so no synchronisation is involved): a load into a
+// register would have to be waited for as soon as the register is copied, one tile later.
+constexpr int G3_RING_SLOTS = 4;
+constexpr int G3_RING_BYTES = (G3_PROD_WARPS + 2 * G3_EPI_WARPS) * G3_RING_SLOTS * 128;
 
 struct G3Shared {
   uint64_t full[G3_MAX_STAGES];   // stage landed (one hardware arrival per producer thread)
@@ -104,7 +109,8 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
   uint8_t* sW = smem;                                      // n_wbuf weight operands
   uint8_t* sStage = sW + (size_t)cfg.n_wbuf * cfg.w_bytes;  // gather ring
   uint8_t* sPatch = sStage + (size_t)cfg.n_stage * G3_STAGE_BYTES;
-  G3Shared* sh = reinterpret_cast<G3Shared*>(sPatch + G3_PATCH_BYTES);
+  uint8_t* sRing = sPatch + G3_PATCH_BYTES;
+  G3Shared* sh = reinterpret_cast<G3Shared*>(sRing + G3_RING_BYTES);
   int* tile_start = reinterpret_cast<int*>(reinterpret_cast<uint8_t*>(sh) + G3_SHARED_BYTES);  // [k_vol + 2]
   int* kpos_s = tile_start + p.k_vol + 2;                                                        // [k_vol + 1]
 
@@ -128,14 +134,15 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     sh->abort_flag = 0;
     mbar_fence_init();
   }
-  for (int s = tid; s <= p.k_vol; s += G3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
-  build_tile_table(G3_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
+  // TMEM allocation overlaps the first global loads below
   uint32_t tmem_cols = 32;
   while (tmem_cols < (uint32_t)cfg.n_tbuf * p.n_dim) tmem_cols <<= 1;
   if (warp == G3_MMA_WARP) {
     tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
     tmem_relinquish();
   }
+  for (int s = tid; s <= p.k_vol; s += G3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
+  build_tile_table(G3_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -166,12 +173,13 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       const uint32_t r = (uint32_t)(16 * pw + rsub + 4 * j);
       a_dst[j] = (r >> 3) * 1024u + (r & 7u) * 128u + (((uint32_t)pc ^ (r & 7u)) << 4);
     }
-    auto load_entry = [&](const G3Walk& w) -> int {
+    const uint32_t ring = smem_u32(sRing) + (uint32_t)(pw * G3_RING_SLOTS * 128 + lane * 4);  // this lane's word of slot 0
+    auto fetch_entry = [&](const G3Walk& w, int slot) {
       const G3Tile ti = g3_tile(w, p, kpos_s);
       const int row = 16 * pw + (lane & 15);
-      if (row >= ti.cnt) return -1;
-      if (ti.dense) return ti.base + row;
-      return __ldg((lane < 16 ? p.gather_map : p.scatter_map) + ti.base + row);
+      const uint32_t dst = ring + (uint32_t)slot * 128u;
+      if (row < ti.cnt && !ti.dense) cp_async4(dst, (lane < 16 ? p.gather_map : p.scatter_map) + ti.base + row);
+      else st_shared_i32(dst, row < ti.cnt ? ti.base + row : -1);
     };
     auto load_weights = [&](int widx, int wb) {
       const uint8_t* wk = wts + (size_t)widx * p.c_in * p.c_out * ES;
@@ -198,18 +206,22 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     G3Walk cur, pf;
     cur.init(tile_start, n_seg, t0);
     pf = cur;
-    int e0 = load_entry(pf), e1 = -1;
+    fetch_entry(pf, 0);
+    cp_async_commit();
     pf.next(tile_start, n_seg);
-    if (pf.t < t1) e1 = load_entry(pf);
+    if (pf.t < t1) fetch_entry(pf, 1);
+    cp_async_commit();
     pf.next(tile_start, n_seg);
     int s = 0;
     uint32_t ph = 0;          // stage and its phase
     int cur_w = -1, n_load = -1, wb = 0;
 
     for (int t = t0; t < t1 && ok; ++t) {
-      int e2 = -1;
-      if (pf.t < t1) e2 = load_entry(pf);
+      if (pf.t < t1) fetch_entry(pf, (t - t0 + 2) & (G3_RING_SLOTS - 1));
+      cp_async_commit();  // also closes the group of the previous tile's gathers
       pf.next(tile_start, n_seg);
+      cp_async_wait<2>();  // everything older than the last two groups has landed: this tile's entries have
+      const int e0 = ld_shared_i32(ring + (uint32_t)((t - t0) & (G3_RING_SLOTS - 1)) * 128u);
       const G3Tile ti = g3_tile(cur, p, kpos_s);
       bool new_w = false;
       if (ti.widx != cur_w) {
@@ -246,8 +258,6 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
         cp_async_arrive_noinc(smem_u32(&sh->full[s]));
         if (++s == n_stage) { s = 0; ph ^= 1u; }
       }
-      e0 = e1;
-      e1 = e2;
       cur.next(tile_start, n_seg);
     }
   } else if (warp == G3_MMA_WARP) {
@@ -318,32 +328,42 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     const uint32_t sw7 = (uint32_t)(lane & 7);
     const uint32_t ch = (uint32_t)(lane & 7), rsub = (uint32_t)(lane >> 3);  // red: chunk ch of rows rsub + 4 u
     // map entries of tile row 32 q + lane (-1 beyond the tile)
-    auto load_entries = [&](const G3Walk& w, int* g, int* sc) {
+    const uint32_t ring = smem_u32(sRing) + (uint32_t)((G3_PROD_WARPS + 2 * warp) * G3_RING_SLOTS * 128 + lane * 4);
+    auto fetch_entries = [&](const G3Walk& w, int slot) {  // gather entry -> ring[slot], scatter entry -> ring[SLOTS + slot]
       const G3Tile ti = g3_tile(w, p, kpos_s);
       const int row = 32 * q4 + lane;
-      *g = -1;
-      *sc = -1;
-      if (row < ti.cnt) {
-        if (ti.dense) { *g = ti.base + row; *sc = ti.base + row; }
-        else { *g = __ldg(p.gather_map + ti.base + row); *sc = __ldg(p.scatter_map + ti.base + row); }
+      const uint32_t dg = ring + (uint32_t)slot * 128u, ds = dg + G3_RING_SLOTS * 128u;
+      if (row < ti.cnt && !ti.dense) {
+        cp_async4(dg, p.gather_map + ti.base + row);
+        cp_async4(ds, p.scatter_map + ti.base + row);
+      } else {
+        const int v = row < ti.cnt ? ti.base + row : -1;
+        st_shared_i32(dg, v);
+        st_shared_i32(ds, v);
       }
     };
     if (t0 + grp < t1) {
       G3Walk pf;
       pf.init(tile_start, n_seg, t0 + grp);
-      int g0, s0, g1 = -1, s1 = -1;
-      load_entries(pf, &g0, &s0);
+      fetch_entries(pf, 0);
+      cp_async_commit();
       pf.next(tile_start, n_seg);
       pf.next(tile_start, n_seg);
-      if (pf.t < t1) load_entries(pf, &g1, &s1);
+      if (pf.t < t1) fetch_entries(pf, 1);
+      cp_async_commit();
       pf.next(tile_start, n_seg);
       pf.next(tile_start, n_seg);
+      int own_i = 0;  // tiles of this group so far
       for (int t = t0 + grp; t < t1 && ok; t += 2) {
         const int tile_i = t - t0;
-        int g2 = -1, s2 = -1;
-        if (pf.t < t1) load_entries(pf, &g2, &s2);
+        if (pf.t < t1) fetch_entries(pf, (own_i + 2) & (G3_RING_SLOTS - 1));
+        cp_async_commit();
         pf.next(tile_start, n_seg);
         pf.next(tile_start, n_seg);
+        cp_async_wait<2>();  // this tile's entries (fetched two of the group's tiles ago) have landed
+        const uint32_t slot = (uint32_t)(own_i & (G3_RING_SLOTS - 1));
+        const int g0 = ld_shared_i32(ring + slot * 128u), s0 = ld_shared_i32(ring + (G3_RING_SLOTS + slot) * 128u);
+        ++own_i;
         const int srow = pair_ok(g0, s0) ? s0 : -1;  // an entry outside the tensors: the pair is skipped
         const int buf = tile_i & (cfg.n_tbuf - 1);
         const uint32_t use = (uint32_t)tile_i >> cfg.tbuf_shift;
@@ -399,8 +419,6 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
           }
           __syncwarp();
         }
-        g0 = g1; s0 = s1;
-        g1 = g2; s1 = s2;
       }
     }
   }
@@ -432,7 +450,7 @@ inline int launch_umma_gms3(const GmsParams& p, bool trans, bool f16, cudaStream
   cfg.n_tbuf = (4 * p.n_dim <= 512) ? 4 : 2;
   cfg.tbuf_shift = cfg.n_tbuf == 4 ? 2 : 1;
   const int table = ((2 * p.k_vol + 3) * 4 + 15) & ~15;
-  const int fixed = 1024 + G3_PATCH_BYTES + G3_SHARED_BYTES + table;
+  const int fixed = 1024 + G3_PATCH_BYTES + G3_RING_BYTES + G3_SHARED_BYTES + table;
   // two weight buffers if at least four gather stages still fit beside them
   cfg.n_wbuf = (fixed + 2 * cfg.w_bytes + 4 * G3_STAGE_BYTES <= max_smem) ? 2 : 1;
   cfg.n_stage = (max_smem - fixed - cfg.n_wbuf * cfg.w_bytes) / G3_STAGE_BYTES;

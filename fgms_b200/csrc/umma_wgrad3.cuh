@@ -102,14 +102,15 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     sh->abort_flag = 0;
     mbar_fence_init();
   }
-  for (int s = tid; s <= p.k_vol; s += W3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
-  build_tile_table(pb, p.kpos, p.k_vol, 0, tile_start);  // syncs the CTA
+  // TMEM allocation overlaps the first global loads below
   uint32_t tmem_cols = 32;
   while (tmem_cols < buf_cols * (uint32_t)cfg.n_buf) tmem_cols <<= 1;
   if (warp == W3_MMA_WARP) {
     tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
     tmem_relinquish();
   }
+  for (int s = tid; s <= p.k_vol; s += W3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
+  build_tile_table(pb, p.kpos, p.k_vol, 0, tile_start);  // syncs the CTA
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
