@@ -193,7 +193,9 @@ def run_ours(args):
         if record: e[1].record()
         backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
         if record: e[2].record()
-        if p.dtype == torch.float16:
+        if p.dtype == torch.float16 and world == 1:
+            backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80)
+        elif p.dtype == torch.float16:
             ws = backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80, accumulate=False)
             part = ws[: w_grad.numel()]
             if world > 1:

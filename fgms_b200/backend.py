@@ -147,7 +147,9 @@ def fgms_bwd_cuda(out_feats_grad, in_feats, kernel, sum_nnz, in_feats_grad, kern
         if out_feats_grad.size(1) != kernel.size(2):
             raise ValueError("out_feats_grad width differs from the kernel's output channels")
     dtype, math = _dtype_math(in_feats, arch80)
-    ws = wgrad_workspace(kernel.size(1), kernel.size(2), k_vol, in_feats.device) if dtype == _lib.DTYPE_F16 else None
+    ws = None
+    if dtype == _lib.DTYPE_F16 and not _single_launch_wgrad(kernel.size(1), kernel.size(2), in_feats.dtype, arch80, None):
+        ws = wgrad_workspace(kernel.size(1), kernel.size(2), k_vol, in_feats.device)
     with torch.cuda.device(in_feats.device):
         _lib.check(_L.fgms_b200_bwd(
             _ptr(out_feats_grad), _ptr(in_feats), _ptr(kernel), _ptr(in_feats_grad), _ptr(kernel_grad), _ptr(kpos),
@@ -168,10 +170,24 @@ def fgms_dgrad_cuda(out_feats_grad, kernel, in_feats_grad, kpos, in_map, out_map
             _stream()))
 
 
+# fp16 weight gradients: False = single launch, every CTA adds its fp32 partial sums (rounded to fp16) into
+# ``kernel_grad`` with fp16 atomics; True = fp32 sums in a workspace, added to ``kernel_grad`` once at the
+# end (three launches).  ``fgms_bwd_cuda`` keeps the reference's signature and follows this switch.
+WGRAD_FP32_SUMS = False
+
+
+def _single_launch_wgrad(c_in, c_out, dtype, arch80, fp32_sums) -> bool:
+    want_fp32 = WGRAD_FP32_SUMS if fp32_sums is None else fp32_sums
+    return dtype == torch.float16 and not want_fp32 and kernel_family("wgrad", c_in, c_out, dtype, arch80) == "tcgen05"
+
+
 def fgms_wgrad_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map, out_map, arch80,
-                    workspace=None, accumulate=True):
+                    workspace=None, accumulate=True, fp32_sums=None):
     """Weight gradient alone (second half of ``ConvolutionBackward``, ``backend/spconv.cu:495-569``).
-    For fp16 the fp32 partial sums of this call are left in ``workspace`` (returned)."""
+
+    fp16 storage: with ``accumulate`` and without ``fp32_sums`` (default: ``WGRAD_FP32_SUMS``) and without
+    a ``workspace`` the single-launch form runs and ``None`` is returned; otherwise the fp32 sums of this
+    call are left in ``workspace`` (returned), which is what a data-parallel caller all-reduces."""
     k_vol = kernel_grad.size(0)
     _check_feat("in_feats", in_feats)
     _check_feat("out_feats_grad", out_feats_grad, in_feats.dtype)
@@ -180,7 +196,9 @@ def fgms_wgrad_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map, out_map
     _check_index("in_map", in_map, in_feats.device)
     _check_index("out_map", out_map, in_feats.device)
     dtype, math = _dtype_math(in_feats, arch80)
-    if dtype == _lib.DTYPE_F16 and workspace is None:
+    single = workspace is None and accumulate and _single_launch_wgrad(kernel_grad.size(1), kernel_grad.size(2),
+                                                                       in_feats.dtype, arch80, fp32_sums)
+    if dtype == _lib.DTYPE_F16 and workspace is None and not single:
         workspace = wgrad_workspace(kernel_grad.size(1), kernel_grad.size(2), k_vol, in_feats.device)
     with torch.cuda.device(in_feats.device):
         _lib.check(_L.fgms_b200_wgrad(

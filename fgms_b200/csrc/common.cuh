@@ -40,6 +40,9 @@ struct WgradParams {
   const int32_t* in_map;
   const int32_t* out_map;
   int n_in, n_out, c_in, c_out, k_vol;
+  // fp16 storage, tensor-core kernel only: add every CTA's fp32 partial sums, rounded to fp16, straight
+  // into the fp16 gradient (dw is then unused)
+  __half* dw_f16 = nullptr;
 };
 
 // ---------------------------------------------------------------------------------------------

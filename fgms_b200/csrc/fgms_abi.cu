@@ -231,6 +231,11 @@ int fgms_b200_wgrad_finalize(void* kernel_grad_f16, const void* workspace_f32, i
   return check_launch("wgrad_finalize_kernel");
 }
 
+static int wgrad_design() {
+  static const int design = [] { const char* e = getenv("FGMS_B200_WGRAD_DESIGN"); return e ? atoi(e) : 3; }();
+  return design;
+}
+
 int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_grad,
                     const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in,
                     int n_out, int c_in, int c_out, int k_vol, int dtype, int math, void* workspace,
@@ -245,7 +250,13 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   const size_t count = (size_t)k_vol * c_in * c_out;
 
   float* acc = nullptr;
-  if (dtype == FGMS_DTYPE_F16) {
+  // fp16 storage, no workspace: every CTA adds its fp32 partial sums, rounded to fp16, straight into
+  // kernel_grad (one launch, no clearing, no second kernel); only the tensor-core kernel does that
+  const bool direct_f16 = dtype == FGMS_DTYPE_F16 && workspace == nullptr && accumulate_into_kernel_grad &&
+                          kernel_grad != nullptr && use_umma(c_in, c_out, dtype, math) && wgrad_design() != 1;
+  if (direct_f16) {
+    // nothing to prepare
+  } else if (dtype == FGMS_DTYPE_F16) {
     const size_t need = fgms_b200_wgrad_workspace_bytes(c_in, c_out, k_vol, dtype);
     if (!workspace || workspace_bytes < need)
       return fail(FGMS_ERR_WORKSPACE, "wgrad needs a %zu-byte workspace for fp16 storage (got %zu)", need,
@@ -265,11 +276,12 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   p.feats = in_feats; p.out_grad = out_grad; p.dw = acc; p.kpos = kpos;
   p.in_map = in_map; p.out_map = out_map;
   p.n_in = n_in; p.n_out = n_out; p.c_in = c_in; p.c_out = c_out; p.k_vol = k_vol;
+  if (direct_f16) p.dw_f16 = static_cast<__half*>(kernel_grad);
 
   bool launched = false;
 #ifndef FGMS_NO_UMMA
   if (use_umma(c_in, c_out, dtype, math)) {
-    static const int design = [] { const char* e = getenv("FGMS_B200_WGRAD_DESIGN"); return e ? atoi(e) : 3; }();
+    const int design = wgrad_design();
     int rc = design == 1 ? fgms::launch_umma_wgrad(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin)
                          : fgms::launch_umma_wgrad3(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
     if (rc == 0) {
@@ -280,6 +292,8 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
     }
   }
 #endif
+  if (!launched && direct_f16)
+    return fail(FGMS_ERR_WORKSPACE, "this shape does not fit the tensor-core weight-gradient kernel: pass a workspace");
   if (!launched) {
     const size_t dyn = (size_t)(k_vol + 2) * sizeof(int);
     const int grid = di.sms * 4;
@@ -293,7 +307,7 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
     }
     if (int rc = check_launch("simt_wgrad_kernel")) return rc;
   }
-  if (dtype == FGMS_DTYPE_F16 && accumulate_into_kernel_grad)
+  if (dtype == FGMS_DTYPE_F16 && accumulate_into_kernel_grad && !direct_f16)
     return fgms_b200_wgrad_finalize(kernel_grad, workspace, (int64_t)count, stream);
   return FGMS_OK;
 }

@@ -279,6 +279,41 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
       if (!ok) break;
       tc_fence_after();
       float* dwk = p.dw + (size_t)seg * p.c_in * p.c_out;
+      if (!TF32 && p.dw_f16 != nullptr) {
+        // fp16 destination: 64 columns (128 bytes of fp16) of the warp's 32 rows per round
+        __half* dwk16 = p.dw_f16 + (size_t)seg * p.c_in * p.c_out;
+        for (int mt = 0; mt < cfg.n_mtile; ++mt) {
+          const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out;
+          for (int c0 = 0; c0 < p.c_out; c0 += 64) {
+#pragma unroll
+            for (int half_i = 0; half_i < 2; ++half_i) {
+              uint32_t v0[16], v1[16], h[16];
+              tmem_ld16(taddr + c0 + 32 * half_i, v0);
+              tmem_ld16(taddr + c0 + 32 * half_i + 16, v1);
+              tmem_ld_wait();
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                h[k] = pack_half2(__uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
+                h[8 + k] = pack_half2(__uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
+              }
+#pragma unroll
+              for (int k = 0; k < 4; ++k)
+                *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)(4 * half_i + k) ^ sw7) << 4)) = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (uint32_t u = 0; u < 8; ++u) {
+              const uint32_t r = rsub + 4 * u;
+              int m;
+              if (cfg.mtile_m == 128) m = mt * 128 + warp * 32 + (int)r;
+              else m = r < 16 ? warp * 16 + (int)r : -1;
+              const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
+              if (m >= 0 && m < p.c_in) red_add_h8(dwk16 + (size_t)m * p.c_out + c0 + (ch << 3), v.x, v.y, v.z, v.w);
+            }
+            __syncwarp();
+          }
+        }
+      } else
       for (int mt = 0; mt < cfg.n_mtile; ++mt) {
         const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out;
         for (int c0 = 0; c0 < p.c_out; c0 += 32) {
@@ -353,7 +388,7 @@ inline bool w3_config(int c_in, int c_out, int es, int max_smem, int k_vol, int 
 // host launcher: 0 launched, 1 shape or pointers do not fit (caller takes the CUDA-core path), < 0 CUDA error
 inline int launch_umma_wgrad3(const WgradParams& p, bool f16, cudaStream_t st, int sms, int max_smem) {
   const int es = f16 ? 2 : 4;
-  if ((reinterpret_cast<uintptr_t>(p.feats) | reinterpret_cast<uintptr_t>(p.out_grad) | reinterpret_cast<uintptr_t>(p.dw)) & 15) return 1;
+  if ((reinterpret_cast<uintptr_t>(p.feats) | reinterpret_cast<uintptr_t>(p.out_grad) | reinterpret_cast<uintptr_t>(p.dw) | reinterpret_cast<uintptr_t>(p.dw_f16)) & 15) return 1;
   W3Config cfg;
   static const int pb_cap = [] { const char* e = getenv("FGMS_B200_WGRAD_PB"); const int v = e ? atoi(e) : W3_MAX_PB; return (v == 32 || v == 64 || v == 128) ? v : W3_MAX_PB; }();
   if (!w3_config(p.c_in, p.c_out, es, max_smem, p.k_vol, pb_cap, &cfg)) return 1;

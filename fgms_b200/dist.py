@@ -62,6 +62,13 @@ def shard_pairs_by_rows(km: KernelMap, world: int, by: str = "out"):
     return shards, bounds
 
 
+def world_size(group=None) -> int:
+    """Ranks in ``group`` (1 outside an initialised process group)."""
+    import torch.distributed as dist
+
+    return dist.get_world_size(group) if dist.is_available() and dist.is_initialized() else 1
+
+
 def allreduce_sum_(tensor, group=None):
     """In-place sum over all ranks; a no-op outside an initialised process group."""
     import torch.distributed as dist
@@ -91,7 +98,10 @@ class SceneParallelLayer:
         import torch
         from . import backend
         backend.fgms_dgrad_cuda(grad_out, weights, in_grad, self.kpos, self.imap, self.omap, self.arch80)
-        if feats.dtype == torch.float16:
+        if feats.dtype == torch.float16 and world_size(self.group) == 1:
+            # nothing to exchange: the kernel adds its fp32 sums into w_grad itself
+            backend.fgms_wgrad_cuda(feats, grad_out, w_grad, self.kpos, self.imap, self.omap, self.arch80)
+        elif feats.dtype == torch.float16:
             ws = backend.fgms_wgrad_cuda(feats, grad_out, w_grad, self.kpos, self.imap, self.omap, self.arch80,
                                          accumulate=False)
             part = ws[: w_grad.numel()]

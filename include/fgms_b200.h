@@ -93,7 +93,13 @@ int fgms_b200_dgrad(const void* out_grad, const void* kernel, void* in_grad, con
  * is what a multi-GPU caller all-reduces) and are then added to kernel_grad; for fp32 storage
  * workspace may be NULL and kernel_grad is accumulated directly.
  * accumulate_into_kernel_grad == 0 leaves kernel_grad untouched (fp16 only): the caller reduces
- * the workspace across ranks and calls fgms_b200_wgrad_finalize itself. */
+ * the workspace across ranks and calls fgms_b200_wgrad_finalize itself.
+ * fp16 storage with workspace == NULL and accumulate_into_kernel_grad != 0 selects the single-launch
+ * form for channel counts the tensor-core kernel covers (fgms_b200_kernel_family(2, ...) == 1): every
+ * CTA sums its share of an offset's pairs in fp32 and adds that partial sum, rounded to fp16, straight
+ * into kernel_grad with fp16 atomics — no clearing, no second kernel, a few fp16 roundings per value
+ * (the reference accumulates every product in fp16, backend/spconv.cu:495-548).  Other channel counts
+ * return FGMS_ERR_WORKSPACE without a workspace. */
 int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_grad,
                     const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in,
                     int n_out, int c_in, int c_out, int k_vol, int dtype, int math, void* workspace,

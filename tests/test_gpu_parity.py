@@ -160,3 +160,31 @@ def test_out_of_range_map_entries_are_skipped_and_counted(mode):
     from oracle import spconv_oracle as orc
     ref = orc.fwd(p.f_np, p.w_np, p.km.n_out, kpos, p.km.imap[keep], p.km.omap[keep])
     assert err(out, ref) <= TOL[mode]
+
+
+@pytest.mark.parametrize("c_in,c_out", [(64, 64), (128, 128), (64, 128), (256, 128)])
+def test_fp16_wgrad_both_forms(c_in, c_out):
+    """fp16 weight gradient: the single-launch form (fp16 atomics across CTAs) and the fp32-workspace form
+    agree with the oracle, accumulate into kernel_grad, and the workspace form leaves the fp32 sums behind."""
+    from fgms_b200 import backend
+    p = Problem(_sub_map(3000, 20, 31), c_in, c_out, seed=9, mode="fp16")
+    assert backend.kernel_family("wgrad", c_in, c_out, torch.float16) == "tcgen05"
+    ref = p.ref_wgrad()
+    prior = (torch.randn_like(p.weights) * 0.5)
+    for fp32_sums in (False, True):
+        w_grad = prior.clone()
+        ws = backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, True, fp32_sums=fp32_sums)
+        assert (ws is None) == (not fp32_sums)
+        e = err(w_grad.float() - prior.float(), ref)
+        assert e <= TOL["fp16"], f"fp32_sums={fp32_sums}: error {e}"
+        if fp32_sums:
+            sums = ws[: w_grad.numel()].view_as(w_grad)
+            assert err(sums, ref) <= 1e-3
+    # the reference-shaped entry point follows the module switch
+    for flag in (False, True):
+        backend.WGRAD_FP32_SUMS = flag
+        try:
+            _, w_grad = p.run_bwd()
+        finally:
+            backend.WGRAD_FP32_SUMS = False
+        assert err(w_grad, ref) <= TOL["fp16"]
