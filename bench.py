@@ -186,13 +186,15 @@ def run_ours(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     pass_ms = {"fwd": [], "dgrad": [], "wgrad": []}
 
-    def step(record):
+    def step(record, passes=False):
+        """One fwd + dgrad + wgrad.  record: events around the step; passes: also between the passes (used in a
+        separate loop only, so that the headline step has nothing between its kernels)."""
         e = [ev() for _ in range(4)] if record else None
         if record: e[0].record()
         layer.forward(p.feats, p.weights, out)
-        if record: e[1].record()
+        if passes: e[1].record()
         backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
-        if record: e[2].record()
+        if passes: e[2].record()
         if p.dtype == torch.float16 and world == 1:
             backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80)
         elif p.dtype == torch.float16:
@@ -228,11 +230,18 @@ def run_ours(args):
         barrier()
     launches = backend.launch_count() - launches0
     step_ms = [e[0].elapsed_time(e[3]) for e in events]
-    for e in events:
+    total_ms = sum(step_ms)
+
+    # per-pass durations (for the roofline of the slowest pass): same steps with events between the passes
+    pass_events = []
+    for _ in range(min(args.steps, 50)):
+        prepare()
+        pass_events.append(step(True, passes=True))
+    barrier()
+    for e in pass_events:
         pass_ms["fwd"].append(e[0].elapsed_time(e[1]))
         pass_ms["dgrad"].append(e[1].elapsed_time(e[2]))
         pass_ms["wgrad"].append(e[2].elapsed_time(e[3]))
-    total_ms = sum(step_ms)
 
     # warm-L2 variant (no flush), reported beside the headline
     for _ in range(2):

@@ -4,6 +4,7 @@
 // operand layouts.  All waits are bounded: a wait that runs out returns false and the caller
 // reports it instead of spinning forever.
 #pragma once
+#include <cstdlib>
 
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -55,6 +56,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   if (abort_flag) *abort_flag = 1;
   return false;
 }
+
+// ------------------------------------------------------------------ programmatic dependent launch
+// A kernel launched with the programmatic-stream-serialization attribute may start while the kernel before
+// it in the stream is still running.  griddep_wait() returns once that kernel has finished and its writes
+// are visible: nothing it may have written (or may still read and this kernel overwrites) is touched
+// before the call.  griddep_launch_dependents() lets the next such kernel in the stream start its own
+// preamble as soon as this grid's CTAs make room.  Both do nothing in a kernel launched the plain way.
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ------------------------------------------------------------------ cp.async (16-byte, zero fill)
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void* src, bool valid) {
@@ -225,4 +235,21 @@ __host__ __device__ constexpr uint32_t mnmajor32_offset(uint32_t k, uint32_t byt
 }
 
 }  // namespace umma
+
+// Launch with the programmatic-stream-serialization attribute (environment FGMS_B200_PDL=0: plain launch).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st, Args... args) {
+  static const bool pdl = [] { const char* e = getenv("FGMS_B200_PDL"); return !(e && e[0] == '0'); }();
+  cudaLaunchConfig_t lc = {};
+  lc.gridDim = dim3((unsigned)grid);
+  lc.blockDim = dim3((unsigned)block);
+  lc.dynamicSmemBytes = smem;
+  lc.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  lc.attrs = at;
+  lc.numAttrs = pdl ? 1 : 0;
+  return cudaLaunchKernelEx(&lc, kernel, static_cast<KArgs>(args)...);
+}
 }  // namespace fgms

@@ -141,6 +141,9 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
     tmem_relinquish();
   }
+  // everything above touches no global memory; from here on the previous kernel's results may be needed
+  griddep_wait();
+  griddep_launch_dependents();
   for (int s = tid; s <= p.k_vol; s += G3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
   build_tile_table(G3_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
   tc_fence_before();
@@ -459,11 +462,11 @@ inline int launch_umma_gms3(const GmsParams& p, bool trans, bool f16, cudaStream
   const int smem = fixed + cfg.n_wbuf * cfg.w_bytes + cfg.n_stage * G3_STAGE_BYTES;
   int rc;
   if (f16) {
-    if (trans) { rc = g3_ensure_smem(umma_gms3_kernel<false, true>, max_smem, 0); if (rc) return rc; umma_gms3_kernel<false, true><<<sms, G3_THREADS, smem, st>>>(p, cfg); }
-    else       { rc = g3_ensure_smem(umma_gms3_kernel<false, false>, max_smem, 1); if (rc) return rc; umma_gms3_kernel<false, false><<<sms, G3_THREADS, smem, st>>>(p, cfg); }
+    if (trans) { rc = g3_ensure_smem(umma_gms3_kernel<false, true>, max_smem, 0); if (rc) return rc; if (launch_pdl(umma_gms3_kernel<false, true>, sms, G3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1; }
+    else       { rc = g3_ensure_smem(umma_gms3_kernel<false, false>, max_smem, 1); if (rc) return rc; if (launch_pdl(umma_gms3_kernel<false, false>, sms, G3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1; }
   } else {
-    if (trans) { rc = g3_ensure_smem(umma_gms3_kernel<true, true>, max_smem, 2); if (rc) return rc; umma_gms3_kernel<true, true><<<sms, G3_THREADS, smem, st>>>(p, cfg); }
-    else       { rc = g3_ensure_smem(umma_gms3_kernel<true, false>, max_smem, 3); if (rc) return rc; umma_gms3_kernel<true, false><<<sms, G3_THREADS, smem, st>>>(p, cfg); }
+    if (trans) { rc = g3_ensure_smem(umma_gms3_kernel<true, true>, max_smem, 2); if (rc) return rc; if (launch_pdl(umma_gms3_kernel<true, true>, sms, G3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1; }
+    else       { rc = g3_ensure_smem(umma_gms3_kernel<true, false>, max_smem, 3); if (rc) return rc; if (launch_pdl(umma_gms3_kernel<true, false>, sms, G3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1; }
   }
   return 0;
 }

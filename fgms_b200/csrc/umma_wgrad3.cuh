@@ -109,6 +109,9 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
     tmem_relinquish();
   }
+  // everything above touches no global memory; from here on the previous kernel's results may be needed
+  griddep_wait();
+  griddep_launch_dependents();
   for (int s = tid; s <= p.k_vol; s += W3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
   build_tile_table(pb, p.kpos, p.k_vol, 0, tile_start);  // syncs the CTA
   tc_fence_before();
@@ -402,13 +405,13 @@ inline int launch_umma_wgrad3(const WgradParams& p, bool f16, cudaStream_t st, i
       if (cudaFuncSetAttribute(umma_wgrad3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) return -1;
       granted[0][dev] = max_smem;
     }
-    umma_wgrad3_kernel<false><<<sms, W3_THREADS, smem, st>>>(p, cfg);
+    if (launch_pdl(umma_wgrad3_kernel<false>, sms, W3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1;
   } else {
     if (granted[1][dev] < max_smem) {
       if (cudaFuncSetAttribute(umma_wgrad3_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) return -1;
       granted[1][dev] = max_smem;
     }
-    umma_wgrad3_kernel<true><<<sms, W3_THREADS, smem, st>>>(p, cfg);
+    if (launch_pdl(umma_wgrad3_kernel<true>, sms, W3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1;
   }
   return 0;
 }
