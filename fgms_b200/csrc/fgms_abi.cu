@@ -14,8 +14,6 @@
 #include "common.cuh"
 #include "simt_kernels.cuh"
 #ifndef FGMS_NO_UMMA
-#include "umma_kernels.cuh"
-#include "umma_gms2.cuh"
 #include "umma_gms3.cuh"
 #include "umma_wgrad3.cuh"
 #endif
@@ -124,13 +122,9 @@ int run_gms(bool trans, const void* src, const void* kernel, void* dst, const in
   p.dense_rows = dense_rows; p.dense_weight = dense_weight;
 #ifndef FGMS_NO_UMMA
   if (use_umma(c_in, c_out, dtype, math)) {
-    static const int design = [] { const char* e = getenv("FGMS_B200_GMS_DESIGN"); return e ? atoi(e) : 3; }();
-    const bool f16 = dtype == FGMS_DTYPE_F16;
-    int rc = design == 1 ? fgms::launch_umma_gms(p, trans, f16, st, di.sms, di.max_smem_optin)
-           : design == 2 ? fgms::launch_umma_gms2(p, trans, f16, st, di.sms, di.max_smem_optin)
-                         : fgms::launch_umma_gms3(p, trans, f16, st, di.sms, di.max_smem_optin);
-    if (rc == 0) return check_launch("umma_gms_kernel");
-    if (rc < 0) return fail(FGMS_ERR_CUDA, "umma_gms_kernel setup failed (%d)", rc);
+    int rc = fgms::launch_umma_gms3(p, trans, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
+    if (rc == 0) return check_launch("umma_gms3_kernel");
+    if (rc < 0) return fail(FGMS_ERR_CUDA, "umma_gms3_kernel setup failed (%d)", rc);
     // rc > 0: shape does not fit the tensor-core kernel's shared memory; take the CUDA-core path
   }
 #endif
@@ -231,11 +225,6 @@ int fgms_b200_wgrad_finalize(void* kernel_grad_f16, const void* workspace_f32, i
   return check_launch("wgrad_finalize_kernel");
 }
 
-static int wgrad_design() {
-  static const int design = [] { const char* e = getenv("FGMS_B200_WGRAD_DESIGN"); return e ? atoi(e) : 3; }();
-  return design;
-}
-
 int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_grad,
                     const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in,
                     int n_out, int c_in, int c_out, int k_vol, int dtype, int math, void* workspace,
@@ -253,7 +242,7 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   // fp16 storage, no workspace: every CTA adds its fp32 partial sums, rounded to fp16, straight into
   // kernel_grad (one launch, no clearing, no second kernel); only the tensor-core kernel does that
   const bool direct_f16 = dtype == FGMS_DTYPE_F16 && workspace == nullptr && accumulate_into_kernel_grad &&
-                          kernel_grad != nullptr && use_umma(c_in, c_out, dtype, math) && wgrad_design() != 1;
+                          kernel_grad != nullptr && use_umma(c_in, c_out, dtype, math);
   if (direct_f16) {
     // nothing to prepare
   } else if (dtype == FGMS_DTYPE_F16) {
@@ -281,14 +270,12 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   bool launched = false;
 #ifndef FGMS_NO_UMMA
   if (use_umma(c_in, c_out, dtype, math)) {
-    const int design = wgrad_design();
-    int rc = design == 1 ? fgms::launch_umma_wgrad(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin)
-                         : fgms::launch_umma_wgrad3(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
+    int rc = fgms::launch_umma_wgrad3(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
     if (rc == 0) {
-      if (int rc2 = check_launch("umma_wgrad_kernel")) return rc2;
+      if (int rc2 = check_launch("umma_wgrad3_kernel")) return rc2;
       launched = true;
     } else if (rc < 0) {
-      return fail(FGMS_ERR_CUDA, "umma_wgrad_kernel setup failed (%d)", rc);
+      return fail(FGMS_ERR_CUDA, "umma_wgrad3_kernel setup failed (%d)", rc);
     }
   }
 #endif

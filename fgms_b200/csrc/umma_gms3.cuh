@@ -25,6 +25,11 @@
 
 namespace fgms {
 
+// shapes the tensor-core kernels take: both channel counts fill whole 128-byte spans, at most 256
+inline bool umma_supported(int c_in, int c_out, int elem_bytes) {
+  return (c_in * elem_bytes) % 128 == 0 && (c_out * elem_bytes) % 128 == 0 && c_in <= 256 && c_out <= 256;
+}
+
 constexpr int G3_TILE_M = 128;
 constexpr int G3_EPI_WARPS = 8;
 constexpr int G3_MMA_WARP = 8;
