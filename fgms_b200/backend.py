@@ -11,7 +11,9 @@ Differences from the reference, all deliberate:
   (``backend/spconv.cu:73``);
 * arguments are validated (device, dtype, contiguity, shapes) and raise ``ValueError`` instead
   of reading out of bounds;
-* fp16 accumulates in fp32 (the reference accumulates in fp16, ``backend/fwd_kernels.cuh:66``);
+* fp16 products are accumulated in fp32 inside a tile (the reference accumulates in fp16,
+  ``backend/fwd_kernels.cuh:66``); what crosses CTAs is added with fp16 atomics like the reference's, except
+  in the workspace form of the weight gradient (``WGRAD_FP32_SUMS``), which stays fp32 to the end;
 * ``arch80`` selects the arithmetic for fp32 storage in the backward as well as the forward
   (``True`` → tf32 tensor cores, ``False`` → exact fp32 FFMA); the reference's backward ignores
   the flag and always uses tf32 (``backend/spconv.cu:551-570``).
