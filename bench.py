@@ -186,22 +186,14 @@ def run_ours(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     pass_ms = {"fwd": [], "dgrad": [], "wgrad": []}
 
-    def step(record, passes=False):
-        """One fwd + dgrad + wgrad.  record: events around the step; passes: also between the passes (used in a
-        separate loop only, so that the headline step has nothing between its kernels)."""
-        e = [ev() for _ in range(4)] if record else None
-        if record: e[0].record()
-        layer.forward(p.feats, p.weights, out)
-        if passes: e[1].record()
-        backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
-        if passes: e[2].record()
+    def layer_wgrad():
         if p.dtype == torch.float16 and world == 1:
             backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80)
         elif p.dtype == torch.float16:
-            ws = backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80, accumulate=False)
+            ws = backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80,
+                                         workspace=backend.wgrad_workspace(wl.c_in, wl.c_out, km.k_vol, dev), accumulate=False)
             part = ws[: w_grad.numel()]
-            if world > 1:
-                dist.all_reduce(part)
+            dist.all_reduce(part)
             backend.wgrad_finalize(w_grad, part)
         else:
             part = torch.zeros_like(w_grad)
@@ -209,6 +201,21 @@ def run_ours(args):
             if world > 1:
                 dist.all_reduce(part)
             w_grad.add_(part)
+
+    def step(record, passes=False):
+        """One fwd + dgrad + wgrad.  record: events around the step; passes: also between the passes (used in a
+        separate loop only, so that the headline step has nothing between its kernels)."""
+        e = [ev() for _ in range(4)] if record else None
+        if record: e[0].record()
+        layer.forward(p.feats, p.weights, out)
+        if passes: e[1].record()
+        if world > 1 and not passes:
+            # data parallel: wgrad first, its all-reduce runs beside dgrad (SceneParallelLayer.backward)
+            layer.backward(p.grad_out, p.feats, p.weights, in_grad, w_grad)
+        else:
+            backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
+            if passes: e[2].record()
+            layer_wgrad()
         if record: e[3].record()
         return e
 

@@ -95,21 +95,31 @@ class SceneParallelLayer:
         return out
 
     def backward(self, grad_out, feats, weights, in_grad, w_grad):
+        """wgrad first, so that the all-reduce of its fp32 sums runs beside dgrad."""
         import torch
+        import torch.distributed as dist
         from . import backend
-        backend.fgms_dgrad_cuda(grad_out, weights, in_grad, self.kpos, self.imap, self.omap, self.arch80)
-        if feats.dtype == torch.float16 and world_size(self.group) == 1:
-            # nothing to exchange: the kernel adds its fp32 sums into w_grad itself
+        multi = world_size(self.group) > 1
+        work = part = None
+        if feats.dtype == torch.float16 and not multi:
+            # nothing to exchange: single launch, straight into w_grad
             backend.fgms_wgrad_cuda(feats, grad_out, w_grad, self.kpos, self.imap, self.omap, self.arch80)
         elif feats.dtype == torch.float16:
             ws = backend.fgms_wgrad_cuda(feats, grad_out, w_grad, self.kpos, self.imap, self.omap, self.arch80,
-                                         accumulate=False)
+                                         workspace=backend.wgrad_workspace(w_grad.size(1), w_grad.size(2), w_grad.size(0),
+                                                                           feats.device), accumulate=False)
             part = ws[: w_grad.numel()]
-            allreduce_sum_(part, self.group)
-            backend.wgrad_finalize(w_grad, part)
         else:
             part = torch.zeros_like(w_grad)
             backend.fgms_wgrad_cuda(feats, grad_out, part, self.kpos, self.imap, self.omap, self.arch80)
-            allreduce_sum_(part, self.group)
-            w_grad += part
+        if multi:
+            work = dist.all_reduce(part, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
+        backend.fgms_dgrad_cuda(grad_out, weights, in_grad, self.kpos, self.imap, self.omap, self.arch80)
+        if work is not None:
+            work.wait()
+        if part is not None:
+            if feats.dtype == torch.float16:
+                backend.wgrad_finalize(w_grad, part)
+            else:
+                w_grad += part
         return in_grad, w_grad
