@@ -27,6 +27,13 @@ SIGNATURES = {
     "fgms_b200_wgrad_f16_noalloc": (c_int, [c_void_p] * 6 + [c_int] * 6 + [c_void_p]),
     "fgms_b200_wgrad_workspace_bytes": (c_size_t, [c_int] * 4),
     "fgms_b200_bwd": (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_int64] + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
+    "fgms_b200_map_workspace_bytes": (c_size_t, [c_int] * 3),
+    "fgms_b200_build_submanifold_map": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
+                                                c_void_p, c_void_p]),
+    "fgms_b200_build_strided_map": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                            c_size_t, c_void_p, c_void_p]),
+    "fgms_b200_transpose_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_size_t, c_void_p]),
     "fgms_b200_kernel_family": (c_int, [c_int] * 5),
     "fgms_b200_device_status": (c_int64, [c_int]),
     "fgms_b200_launch_count": (c_int64, []),

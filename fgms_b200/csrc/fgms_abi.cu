@@ -13,6 +13,7 @@
 
 #include "common.cuh"
 #include "simt_kernels.cuh"
+#include "map_builder.cuh"
 #ifndef FGMS_NO_UMMA
 #include "umma_gms3.cuh"
 #include "umma_wgrad3.cuh"
@@ -360,6 +361,130 @@ int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel
 int fgms_b200_kernel_family(int pass, int c_in, int c_out, int dtype, int math) {
   if (pass < 0 || pass > 2 || !dtype_ok(dtype)) return fail(FGMS_ERR_INVALID_ARG, "bad pass or dtype");
   return use_umma(c_in, c_out, dtype, math) ? 1 : 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Kernel maps (csrc/map_builder.cuh)
+// ---------------------------------------------------------------------------------------------
+size_t fgms_b200_map_workspace_bytes(int n, int n_cols, int k_vol) {
+  if (n < 0 || n_cols < 0 || k_vol < 1) return 0;
+  return fgms::maps::layout(n, n_cols, k_vol).total;
+}
+
+namespace {
+struct MapWs {
+  fgms::maps::Layout L;
+  uint8_t* base;
+  fgms::maps::Table table() const {
+    return fgms::maps::Table{reinterpret_cast<unsigned long long*>(base + L.keys), reinterpret_cast<int*>(base + L.vals), L.cap - 1};
+  }
+  int* dense() const { return reinterpret_cast<int*>(base + L.dense); }
+  int* tile_sums() const { return reinterpret_cast<int*>(base + L.tile_sums); }
+  int* counter() const { return reinterpret_cast<int*>(base + L.counter); }
+};
+int map_ws(int n, int n_cols, int k_vol, void* workspace, size_t bytes, MapWs* w) {
+  w->L = fgms::maps::layout(n, n_cols, k_vol);
+  if (!workspace || bytes < w->L.total)
+    return fail(FGMS_ERR_WORKSPACE, "map builder needs a %zu-byte workspace (got %zu)", w->L.total, workspace ? bytes : (size_t)0);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255) return fail(FGMS_ERR_WORKSPACE, "workspace must be 256-byte aligned");
+  w->base = static_cast<uint8_t*>(workspace);
+  return FGMS_OK;
+}
+int blocks_for(long long n, int threads) { return (int)((n + threads - 1) / threads); }
+int cuda_fail(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  return fail(FGMS_ERR_CUDA, "%s: %s", what, cudaGetErrorString(e));
+}
+}  // namespace
+
+int fgms_b200_build_submanifold_map(const int32_t* coords, int n, int kernel_size, int32_t* kpos, int32_t* in_map,
+                                    int32_t* out_map, void* workspace, size_t workspace_bytes, int64_t* pairs_host,
+                                    void* stream) {
+  if (n < 0 || kernel_size < 1 || kernel_size > 7 || kernel_size % 2 == 0)
+    return fail(FGMS_ERR_INVALID_ARG, "n must be >= 0 and kernel_size odd, 1..7");
+  if (!kpos || (n > 0 && (!coords || !in_map || !out_map))) return fail(FGMS_ERR_INVALID_ARG, "null pointer");
+  const int k_vol = kernel_size * kernel_size * kernel_size;
+  if ((long long)k_vol * n > 0x7fffffffll) return fail(FGMS_ERR_INVALID_ARG, "k_vol * n exceeds the int32 range of the maps");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MapWs w;
+  if (int rc = map_ws(n, n, k_vol, workspace, workspace_bytes, &w)) return rc;
+  if (n == 0) {
+    if (cudaMemsetAsync(kpos, 0, (size_t)(k_vol + 1) * 4, st) != cudaSuccess) return cuda_fail("cudaMemsetAsync");
+  } else {
+    if (cudaMemsetAsync(w.base + w.L.keys, 0xff, (size_t)w.L.cap * 8, st) != cudaSuccess) return cuda_fail("cudaMemsetAsync");
+    fgms::maps::insert_kernel<<<blocks_for(n, 256), 256, 0, st>>>(coords, n, 1, w.table(), w.counter());
+    const long long cells = (long long)k_vol * n;
+    fgms::maps::submanifold_fill_kernel<<<blocks_for(cells, 256), 256, 0, st>>>(coords, n, kernel_size, w.table(), w.dense());
+    if (!fgms::maps::finish(w.dense(), k_vol, n, w.tile_sums(), kpos, in_map, out_map, st)) return cuda_fail("map builder launch");
+    g_launches += 5;
+  }
+  if (pairs_host) {
+    int32_t total = 0;
+    if (cudaMemcpyAsync(&total, kpos + k_vol, 4, cudaMemcpyDeviceToHost, st) != cudaSuccess ||
+        cudaStreamSynchronize(st) != cudaSuccess)
+      return cuda_fail("reading the pair count");
+    *pairs_host = total;
+  }
+  return FGMS_OK;
+}
+
+int fgms_b200_build_strided_map(const int32_t* coords, int n, int stride, int32_t* out_coords, int32_t* kpos,
+                                int32_t* in_map, int32_t* out_map, void* workspace, size_t workspace_bytes,
+                                int* n_out_host, void* stream) {
+  if (n < 0 || stride < 2 || stride > 4) return fail(FGMS_ERR_INVALID_ARG, "n must be >= 0 and stride 2..4");
+  if (!kpos || !n_out_host || (n > 0 && (!coords || !out_coords || !in_map || !out_map)))
+    return fail(FGMS_ERR_INVALID_ARG, "null pointer");
+  const int k_vol = stride * stride * stride;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MapWs w;
+  if (int rc = map_ws(n, n, k_vol, workspace, workspace_bytes, &w)) return rc;
+  *n_out_host = 0;
+  if (n == 0) {
+    if (cudaMemsetAsync(kpos, 0, (size_t)(k_vol + 1) * 4, st) != cudaSuccess) return cuda_fail("cudaMemsetAsync");
+    return FGMS_OK;
+  }
+  auto* ukeys = reinterpret_cast<unsigned long long*>(w.base + w.L.ukeys);
+  auto* sorted = reinterpret_cast<unsigned long long*>(w.base + w.L.ukeys_sorted);
+  if (cudaMemsetAsync(w.base + w.L.keys, 0xff, (size_t)w.L.cap * 8, st) != cudaSuccess ||
+      cudaMemsetAsync(w.counter(), 0, 8, st) != cudaSuccess)
+    return cuda_fail("cudaMemsetAsync");
+  // unique parents -> counter[0]; their keys, gathered in table order -> counter[1] counts them again
+  fgms::maps::insert_kernel<<<blocks_for(n, 256), 256, 0, st>>>(coords, n, stride, w.table(), w.counter());
+  fgms::maps::collect_keys_kernel<<<blocks_for(w.L.cap, 256), 256, 0, st>>>(w.table(), ukeys, w.counter() + 1);
+  int n_out = 0;
+  if (cudaMemcpyAsync(&n_out, w.counter(), 4, cudaMemcpyDeviceToHost, st) != cudaSuccess || cudaStreamSynchronize(st) != cudaSuccess)
+    return cuda_fail("reading the number of output voxels");
+  if (n_out < 1 || n_out > n) return fail(FGMS_ERR_DEVICE, "no output voxel could be formed (coordinates out of range?)");
+  size_t cub_bytes = w.L.cub_bytes;
+  if (cub::DeviceRadixSort::SortKeys(w.base + w.L.cub, cub_bytes, ukeys, sorted, n_out, 0, 3 * fgms::maps::COORD_BITS, st) != cudaSuccess)
+    return cuda_fail("radix sort");
+  fgms::maps::rank_kernel<<<blocks_for(n_out, 256), 256, 0, st>>>(sorted, n_out, w.table(), out_coords);
+  const long long cells = (long long)k_vol * n_out;
+  fgms::maps::fill_kernel<<<blocks_for(cells, 256) < 2048 ? blocks_for(cells, 256) : 2048, 256, 0, st>>>(w.dense(), cells, -1);
+  fgms::maps::strided_fill_kernel<<<blocks_for(n, 256), 256, 0, st>>>(coords, n, stride, n_out, w.table(), w.dense());
+  if (!fgms::maps::finish(w.dense(), k_vol, n_out, w.tile_sums(), kpos, in_map, out_map, st)) return cuda_fail("map builder launch");
+  g_launches += 8;
+  *n_out_host = n_out;
+  return FGMS_OK;
+}
+
+int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in, int k_vol,
+                            int64_t pairs, int32_t* kpos_t, int32_t* in_map_t, int32_t* out_map_t, void* workspace,
+                            size_t workspace_bytes, void* stream) {
+  if (n_in < 0 || k_vol < 1 || pairs < 0) return fail(FGMS_ERR_INVALID_ARG, "negative size");
+  if (!kpos || !kpos_t || (pairs > 0 && (!in_map || !out_map || !in_map_t || !out_map_t)))
+    return fail(FGMS_ERR_INVALID_ARG, "null pointer");
+  if ((long long)k_vol * n_in > 0x7fffffffll) return fail(FGMS_ERR_INVALID_ARG, "k_vol * n_in exceeds the int32 range of the maps");
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  MapWs w;
+  if (int rc = map_ws(0, n_in, k_vol, workspace, workspace_bytes, &w)) return rc;
+  const long long cells = (long long)k_vol * n_in;
+  if (cells > 0) fgms::maps::fill_kernel<<<blocks_for(cells, 256) < 2048 ? blocks_for(cells, 256) : 2048, 256, 0, st>>>(w.dense(), cells, -1);
+  if (pairs > 0)
+    fgms::maps::transpose_fill_kernel<<<blocks_for(pairs, 256), 256, 0, st>>>(kpos, in_map, out_map, k_vol, pairs, n_in, w.dense());
+  if (!fgms::maps::finish(w.dense(), k_vol, n_in, w.tile_sums(), kpos_t, in_map_t, out_map_t, st)) return cuda_fail("map builder launch");
+  g_launches += 5;
+  return FGMS_OK;
 }
 
 int64_t fgms_b200_device_status(int reset) {

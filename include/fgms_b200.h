@@ -141,6 +141,45 @@ int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel
                   int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                   int separate_mid, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Kernel maps on the GPU.  No counterpart in the reference, which loads its maps from files
+ * (spconv-test.py:63-73); every caller of the operator needs them, so they are the step right before
+ * the path.  Canonical form, identical to what fgms_b200/maps.py builds on the host: offsets
+ * enumerated lexicographically over (dx, dy, dz) (the centre is k_vol / 2, backend/spconv.cu:52),
+ * pairs offset-major, ascending output row inside an offset.  coords: device int32 [n, 3], every
+ * coordinate in [-2^20 + 8, 2^20 - 8), no voxel twice.  kpos: device int32 [k_vol + 1]; in_map /
+ * out_map: device int32 with room for the most pairs possible (stated per function).  workspace:
+ * 256-byte aligned device memory of fgms_b200_map_workspace_bytes(n, n_cols, k_vol) bytes, where n is
+ * the number of voxels that go into the hash table and n_cols the number of output voxels (an upper
+ * bound is fine).  Bad coordinates and duplicate voxels are skipped and counted
+ * (fgms_b200_device_status).
+ * --------------------------------------------------------------------------------------------- */
+size_t fgms_b200_map_workspace_bytes(int n, int n_cols, int k_vol);
+
+/* Stride-1 submanifold map, kernel_size odd (3 -> 27 offsets): pair (i, o) belongs to offset d iff
+ * coords[i] == coords[o] + d.  in_map / out_map need n * k_vol entries; workspace for (n, n, k_vol).
+ * pairs_host, if not NULL, receives kpos[k_vol] (the call then synchronises the stream). */
+int fgms_b200_build_submanifold_map(const int32_t* coords, int n, int kernel_size, int32_t* kpos,
+                                    int32_t* in_map, int32_t* out_map, void* workspace,
+                                    size_t workspace_bytes, int64_t* pairs_host, void* stream);
+
+/* Downsampling map with kernel_size == stride: output voxels are the distinct floor(coords / stride)
+ * in lexicographic order, written to out_coords (device int32, room for [n, 3]); the offset of a pair
+ * is coords[i] - stride * out_coords[o].  Every input has exactly one pair: in_map / out_map need n
+ * entries; workspace for (n, n, stride^3).  The number of output voxels is returned in *n_out_host;
+ * the call synchronises the stream once to learn it. */
+int fgms_b200_build_strided_map(const int32_t* coords, int n, int stride, int32_t* out_coords,
+                                int32_t* kpos, int32_t* in_map, int32_t* out_map, void* workspace,
+                                size_t workspace_bytes, int* n_out_host, void* stream);
+
+/* Map of the transposed convolution: the same pairs with input and output swapped, re-ordered to
+ * ascending (new) output row inside each offset.  n_in = rows of the ORIGINAL input (the new output);
+ * an input row must not occur twice in one offset.  Outputs need `pairs` entries; workspace for
+ * (0, n_in, k_vol). */
+int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const int32_t* out_map,
+                            int n_in, int k_vol, int64_t pairs, int32_t* kpos_t, int32_t* in_map_t,
+                            int32_t* out_map_t, void* workspace, size_t workspace_bytes, void* stream);
+
 /* Which kernel family the dispatch picks for a shape: 0 = CUDA-core (SIMT), 1 = tcgen05.
  * pass: 0 forward, 1 dgrad, 2 wgrad. */
 int fgms_b200_kernel_family(int pass, int c_in, int c_out, int dtype, int math);
