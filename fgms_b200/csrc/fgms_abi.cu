@@ -97,6 +97,18 @@ bool use_umma(int c_in, int c_out, int dtype, int math) {
   return math != FGMS_MATH_FP32 && umma_shape_ok(c_in, c_out, dtype);
 }
 
+// the weight-gradient kernel tiles fewer row counts than forward / dgrad (c_in a multiple of 128, or 64, or one
+// 128-byte span); the shared-memory size used for the check is the opt-in maximum of sm_100
+bool use_umma_wgrad(int c_in, int c_out, int dtype, int math) {
+#ifdef FGMS_NO_UMMA
+  return false;
+#else
+  if (!use_umma(c_in, c_out, dtype, math)) return false;
+  fgms::W3Config cfg;
+  return fgms::w3_config(c_in, c_out, dtype == FGMS_DTYPE_F16 ? 2 : 4, 232448, 27, fgms::W3_MAX_PB, &cfg);
+#endif
+}
+
 template <typename T, bool TRANS>
 int launch_simt_gms(const fgms::GmsParams& p, cudaStream_t st, int sms) {
   const size_t dyn = (size_t)(p.k_vol + 2) * sizeof(int);
@@ -243,7 +255,7 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   // fp16 storage, no workspace: every CTA adds its fp32 partial sums, rounded to fp16, straight into
   // kernel_grad (one launch, no clearing, no second kernel); only the tensor-core kernel does that
   const bool direct_f16 = dtype == FGMS_DTYPE_F16 && workspace == nullptr && accumulate_into_kernel_grad &&
-                          kernel_grad != nullptr && use_umma(c_in, c_out, dtype, math);
+                          kernel_grad != nullptr && use_umma_wgrad(c_in, c_out, dtype, math);
   if (direct_f16) {
     // nothing to prepare
   } else if (dtype == FGMS_DTYPE_F16) {
@@ -360,6 +372,7 @@ int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel
 
 int fgms_b200_kernel_family(int pass, int c_in, int c_out, int dtype, int math) {
   if (pass < 0 || pass > 2 || !dtype_ok(dtype)) return fail(FGMS_ERR_INVALID_ARG, "bad pass or dtype");
+  if (pass == 2) return use_umma_wgrad(c_in, c_out, dtype, math) ? 1 : 0;
   return use_umma(c_in, c_out, dtype, math) ? 1 : 0;
 }
 

@@ -53,7 +53,7 @@ def test_golden_fixtures_fp32(golden):
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("c_in,c_out", [(1, 1), (3, 5), (4, 32), (16, 16), (17, 33), (32, 64), (64, 32), (64, 64),
-                                        (48, 80), (128, 128), (96, 128), (128, 64), (256, 128), (128, 256)])
+                                        (48, 80), (128, 128), (96, 128), (128, 64), (256, 128), (128, 256), (192, 64)])
 def test_channel_classes_submanifold(mode, c_in, c_out):
     p = Problem(_sub_map(1500, 14, c_in * 131 + c_out), c_in, c_out, seed=c_in + 7 * c_out, mode=mode)
     _check_all(p)
