@@ -424,7 +424,9 @@ int fgms_b200_build_submanifold_map(const int32_t* coords, int n, int kernel_siz
   if (n == 0) {
     if (cudaMemsetAsync(kpos, 0, (size_t)(k_vol + 1) * 4, st) != cudaSuccess) return cuda_fail("cudaMemsetAsync");
   } else {
-    if (cudaMemsetAsync(w.base + w.L.keys, 0xff, (size_t)w.L.cap * 8, st) != cudaSuccess) return cuda_fail("cudaMemsetAsync");
+    if (cudaMemsetAsync(w.base + w.L.keys, 0xff, (size_t)w.L.cap * 8, st) != cudaSuccess ||
+        cudaMemsetAsync(w.base + w.L.vals, 0x7f, (size_t)w.L.cap * 4, st) != cudaSuccess)
+      return cuda_fail("cudaMemsetAsync");
     fgms::maps::insert_kernel<<<blocks_for(n, 256), 256, 0, st>>>(coords, n, 1, w.table(), w.counter());
     const long long cells = (long long)k_vol * n;
     fgms::maps::submanifold_fill_kernel<<<blocks_for(cells, 256), 256, 0, st>>>(coords, n, kernel_size, w.table(), w.dense());

@@ -82,7 +82,8 @@ __device__ __forceinline__ int table_find(const Table& t, unsigned long long key
   return -1;
 }
 
-// coordinate (or its parent under `stride`) of every voxel -> table.  value = row (stride 1).  A
+// coordinate (or its parent under `stride`) of every voxel -> table.  value = row (stride 1; the values start
+// at 0x7f7f7f7f).  A
 // coordinate outside the packable range or met twice (stride 1) is counted as a problem.
 __global__ void insert_kernel(const int32_t* __restrict__ coords, int n, int stride, Table t, int* n_unique) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -95,7 +96,8 @@ __global__ void insert_kernel(const int32_t* __restrict__ coords, int n, int str
   const int slot = table_insert(t, key, &fresh);
   if (slot < 0) { report_problem(); return; }
   if (stride == 1) {
-    if (fresh) t.vals[slot] = i; else report_problem();  // duplicate voxel
+    atomicMin(t.vals + slot, i);     // a voxel met twice keeps its first row, whichever thread got here first
+    if (!fresh) report_problem();    // duplicate voxel
   } else if (fresh) {
     atomicAdd(n_unique, 1);
   }

@@ -104,6 +104,9 @@ __device__ __forceinline__ G3Tile g3_tile(const G3Walk& w, const GmsParams& p, c
   return ti;
 }
 
+// the weight matrix of the walk's tile (needs no table access)
+__device__ __forceinline__ int g3_widx(const G3Walk& w, const GmsParams& p) { return w.seg == p.k_vol ? p.dense_weight : w.seg; }
+
 template <bool TF32, bool TRANS_W>
 __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G3Config cfg) {
   using namespace umma;
@@ -189,24 +192,30 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       if (row < ti.cnt && !ti.dense) cp_async4(dst, (lane < 16 ? p.gather_map : p.scatter_map) + ti.base + row);
       else st_shared_i32(dst, row < ti.cnt ? ti.base + row : -1);
     };
+    // Weight matrix -> operand layout.  The matrix is `w_rows` rows of `cpr` 16-byte chunks; when cpr divides the
+    // number of producer threads every thread keeps one chunk column and strides over rows (no division in the loop).
+    const int w_rows = TRANS_W ? p.n_dim : p.k_dim;
+    const int cpr = (TRANS_W ? p.k_dim : p.n_dim) * ES / 16;
+    const bool cpr_divides = (G3_PROD_THREADS % cpr) == 0;
+    const uint32_t w_c = cpr_divides ? (uint32_t)(tp % cpr) : 0u;
+    const int w_r0 = cpr_divides ? tp / cpr : 0, w_rstep = cpr_divides ? G3_PROD_THREADS / cpr : 0;
+    const uint32_t w_lbo = (uint32_t)p.k_dim * 128u;
+    auto w_offset = [&](uint32_t row, uint32_t c) -> uint32_t {
+      if (TRANS_W) return kmajor_offset(row, c * 16u, p.n_dim);  // rows = output index: K-major operand
+      return TF32 ? mnmajor32_offset(row, c * 16u, w_lbo, 512u) : mnmajor_offset(row, c * 16u, w_lbo, 1024u);  // rows = contraction index: MN-major
+    };
     auto load_weights = [&](int widx, int wb) {
       const uint8_t* wk = wts + (size_t)widx * p.c_in * p.c_out * ES;
       const uint32_t sw = smem_u32(sW + (size_t)wb * cfg.w_bytes);
-      if (!TRANS_W) {
-        // rows = contraction index (k_dim rows of n_dim elements): MN-major operand
-        const int cpr = p.n_dim * ES / 16, total = p.k_dim * cpr;
-        const uint32_t lbo = (uint32_t)p.k_dim * 128u;
-        for (int e = tp; e < total; e += G3_PROD_THREADS) {
-          const uint32_t row = e / cpr, c = e % cpr;
-          const uint32_t off = TF32 ? mnmajor32_offset(row, c * 16u, lbo, 512u) : mnmajor_offset(row, c * 16u, lbo, 1024u);
-          cp_async16(sw + off, wk + (size_t)row * w_row_bytes + c * 16u, true);
-        }
+      if (cpr_divides) {
+        const uint8_t* col = wk + w_c * 16u;
+        for (int row = w_r0; row < w_rows; row += w_rstep)
+          cp_async16(sw + w_offset((uint32_t)row, w_c), col + (size_t)row * w_row_bytes, true);
       } else {
-        // rows = output index (n_dim rows of k_dim elements): K-major operand
-        const int cpr = p.k_dim * ES / 16, total = p.n_dim * cpr;
+        const int total = w_rows * cpr;
         for (int e = tp; e < total; e += G3_PROD_THREADS) {
           const uint32_t row = e / cpr, c = e % cpr;
-          cp_async16(sw + kmajor_offset(row, c * 16u, p.n_dim), wk + (size_t)row * w_row_bytes + c * 16u, true);
+          cp_async16(sw + w_offset(row, c), wk + (size_t)row * w_row_bytes + c * 16u, true);
         }
       }
     };
@@ -228,10 +237,7 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       if (pf.t < t1) fetch_entry(pf, (t - t0 + 2) & (G3_RING_SLOTS - 1));
       cp_async_commit();  // also closes the group of the previous tile's gathers
       pf.next(tile_start, n_seg);
-      cp_async_wait<2>();  // everything older than the last two groups has landed: this tile's entries have
-      const int e0 = ld_shared_i32(ring + (uint32_t)((t - t0) & (G3_RING_SLOTS - 1)) * 128u);
       const G3Tile ti = g3_tile(cur, p, kpos_s);
-      bool new_w = false;
       if (ti.widx != cur_w) {
         // weight load number n_load goes to buffer n_load % n_wbuf, whose previous tenant was load
         // n_load - n_wbuf: wait until the MMA warp has reported that tenant's last MMA finished
@@ -243,25 +249,32 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
           if (!ok) break;
         }
         cur_w = ti.widx;
-        new_w = true;
+        // issued before the wait for this tile's map entries; the first stage's barrier below also covers these copies
+        load_weights(ti.widx, wb);
       }
+      cp_async_wait<2>();  // everything older than the last two groups has landed: this tile's entries have
+      const int e0 = ld_shared_i32(ring + (uint32_t)((t - t0) & (G3_RING_SLOTS - 1)) * 128u);
+      // lanes 0-15 hold gather entries, lanes 16-31 the scatter entries of the same rows: settle once per
+      // pair whether it is used, then one shuffle per row hands out the gather entry (-1: zero-fill)
+      const int other = __shfl_xor_sync(0xffffffffu, e0, 16);
+      const int g_own = lane < 16 ? e0 : other, s_own = lane < 16 ? other : e0;
+      const bool okp = pair_ok(g_own, s_own);
+      if (!okp && lane < 16 && (g_own != -1 || s_own != -1)) report_problem();  // entry outside the tensors: pair skipped, counted once
+      const int ev = okp ? g_own : -1;
       const uint8_t* rsrc[4];
       bool valid[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int r = rsub + 4 * j;
-        const int g = __shfl_sync(0xffffffffu, e0, r), sc = __shfl_sync(0xffffffffu, e0, 16 + r);
-        valid[j] = pair_ok(g, sc);
-        if (!valid[j] && pc == 0 && (g != -1 || sc != -1)) report_problem();  // entry outside the tensors: pair skipped, counted once
-        rsrc[j] = valid[j] ? src + (size_t)g * src_row_bytes + (size_t)pc * 16 : src;
+        const int g = __shfl_sync(0xffffffffu, ev, rsub + 4 * j);
+        valid[j] = g >= 0;
+        rsrc[j] = src + (size_t)max(g, 0) * src_row_bytes + (size_t)pc * 16;
       }
       for (int kc = 0; kc < kch && ok; ++kc) {
         ok = g3_wait(&sh->empty[s], ph ^ 1u, abort_flag);
         if (!ok) break;
-        if (new_w && kc == 0) load_weights(ti.widx, wb);
         const uint32_t st = smem_u32(sStage + (size_t)s * G3_STAGE_BYTES);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) cp_async16(st + a_dst[j], rsrc[j] + (valid[j] ? (size_t)kc * 128 : 0), valid[j]);
+        for (int j = 0; j < 4; ++j) cp_async16(st + a_dst[j], rsrc[j] + (size_t)kc * 128, valid[j]);
         // the stage's barrier hears from this thread when everything it has issued so far has landed
         cp_async_arrive_noinc(smem_u32(&sh->full[s]));
         if (++s == n_stage) { s = 0; ph ^= 1u; }
@@ -279,14 +292,14 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
       const int buf = tile_i & (cfg.n_tbuf - 1);
       const uint32_t use = (uint32_t)tile_i >> cfg.tbuf_shift;
-      const G3Tile ti = g3_tile(cur, p, kpos_s);
-      if (ti.widx != cur_w) {  // same numbering of weight loads as in the producers
+      const int widx = g3_widx(cur, p);
+      if (widx != cur_w) {  // same numbering of weight loads as in the producers
         ++n_load;
         wb = (cfg.n_wbuf == 2) ? (n_load & 1) : 0;
-        cur_w = ti.widx;
+        cur_w = widx;
       }
       cur.next(tile_start, n_seg);
-      const bool last_of_w = (t + 1 == t1) || g3_tile(cur, p, kpos_s).widx != cur_w;
+      const bool last_of_w = (t + 1 == t1) || g3_widx(cur, p) != cur_w;
       ok = g3_wait(&sh->tmem_empty[buf], (use & 1u) ^ 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();

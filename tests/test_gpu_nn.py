@@ -40,7 +40,7 @@ def test_two_layers_share_a_map_and_train():
     for _ in range(3):
         y = l2(torch.relu(l1(x, dk)), dk)
         loss = ((y - target) ** 2).mean()
-        losses.append(float(loss))
+        losses.append(float(loss.detach()))
         for q in params:
             q.grad = None
         loss.backward()
