@@ -44,7 +44,7 @@ UNIT = "TFLOPS"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (kernel -> workload -> bytes); None where no capture exists yet.
 NCU_TRAFFIC = {  # profiles/cfg4_fp16_c128_umma_kernels.md
-    ("fwd", "cfg4"): 80.4e6, ("dgrad", "cfg4"): 79.4e6, ("wgrad", "cfg4"): 81.9e6,
+    ("fwd", "cfg4"): 79.8e6, ("dgrad", "cfg4"): 79.4e6, ("wgrad", "cfg4"): 83.7e6,
 }
 
 
