@@ -157,11 +157,15 @@ def run_ours(args):
     import torch
     import torch.distributed as dist
     from fgms_b200 import backend, workloads
-    from fgms_b200.dist import SceneParallelLayer
+    from fgms_b200.dist import BoundSceneLayer, SceneParallelLayer
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        # the 1.8 MB weight-gradient all-reduce is latency-bound; on this pool's 8-GPU boxes it was measured
+        # faster without NVLink-switch reductions (30.8 vs 46.0 us back to back, 213 vs 228 us per step)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
     torch.cuda.set_device(local)
@@ -186,6 +190,8 @@ def run_ours(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     pass_ms = {"fwd": [], "dgrad": [], "wgrad": []}
 
+    bound = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80) if world > 1 else None
+
     def layer_wgrad():
         if p.dtype == torch.float16 and world == 1:
             backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80)
@@ -207,15 +213,18 @@ def run_ours(args):
         separate loop only, so that the headline step has nothing between its kernels)."""
         e = [ev() for _ in range(4)] if record else None
         if record: e[0].record()
+        if world > 1 and not passes:
+            # data parallel: the step bound to its buffers (no per-call argument checks on the host); wgrad first,
+            # its all-reduce runs beside dgrad
+            bound.forward()
+            bound.backward()
+            if record: e[3].record()
+            return e
         layer.forward(p.feats, p.weights, out)
         if passes: e[1].record()
-        if world > 1 and not passes:
-            # data parallel: wgrad first, its all-reduce runs beside dgrad (SceneParallelLayer.backward)
-            layer.backward(p.grad_out, p.feats, p.weights, in_grad, w_grad)
-        else:
-            backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
-            if passes: e[2].record()
-            layer_wgrad()
+        backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
+        if passes: e[2].record()
+        layer_wgrad()
         if record: e[3].record()
         return e
 
@@ -228,14 +237,41 @@ def run_ours(args):
     for _ in range(args.warmup):
         prepare(); step(False)
     barrier()
+    # The same launches are captured once into a CUDA graph and replayed, which takes the host out of the step;
+    # the kernels, their order and their arguments are those of the eager step.  --no-graph times the eager step.
+    graph = None
+    launches_per_step = None
+    if args.graph and world == 1:  # with a collective in the step, capture hung on this pool: N > 1 runs the bound plan eagerly
+        try:
+            c0 = backend.launch_count()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step(False)
+            launches_per_step = backend.launch_count() - c0
+            graph = g
+            for _ in range(3):
+                prepare(); graph.replay()
+            barrier()
+        except Exception as exc:  # capture not possible: time the eager step
+            sys.stderr.write(f"bench: CUDA graph capture failed ({exc!r}); timing the eager step\n")
+            graph = None
+            torch.cuda.synchronize()
+
+    def timed_step():
+        if graph is None:
+            return step(True)
+        e = [ev() for _ in range(4)]
+        e[0].record(); graph.replay(); e[3].record()
+        return e
+
     launches0 = backend.launch_count()
     events = []
     with ClockSampler(local) as clocks:
         for _ in range(args.steps):
             prepare()
-            events.append(step(True))
+            events.append(timed_step())
         barrier()
-    launches = backend.launch_count() - launches0
+    launches = (backend.launch_count() - launches0) if graph is None else launches_per_step * args.steps
     step_ms = [e[0].elapsed_time(e[3]) for e in events]
     total_ms = sum(step_ms)
 
@@ -257,7 +293,7 @@ def run_ours(args):
     warm = []
     for _ in range(args.steps):
         out.zero_(); in_grad.zero_(); w_grad.zero_()
-        e = step(True)
+        e = timed_step()
         warm.append(e)
     barrier()
     warm_ms = sum(e[0].elapsed_time(e[3]) for e in warm)
@@ -364,7 +400,8 @@ def run_ours(args):
             "ms_per_step": total_ms / k, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"fp16": "f16 (fp32 accumulate)", "tf32": "tf32 (fp32 accumulate)", "fp32": "f32"}[wl.mode],
             "data": "synthetic",
-            "config": workload_config(wl, world, "flushed before every step (512 MB overwrite), outputs re-zeroed, both untimed"),
+            "config": dict(workload_config(wl, world, "flushed before every step (512 MB overwrite), outputs re-zeroed, both untimed"),
+                           launch="CUDA-graph replay of the step's launches" if graph is not None else "eager launches"),
             "e2e": {"value": flops_all * k / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / k},
             "gpu_launches": int(launches),
@@ -401,6 +438,7 @@ def main():
     ap.add_argument("--workload", default="cfg4")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the eager step instead of a CUDA-graph replay of it")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -123,3 +123,71 @@ class SceneParallelLayer:
             else:
                 w_grad += part
         return in_grad, w_grad
+
+
+class BoundSceneLayer:
+    """A :class:`SceneParallelLayer` step bound to fixed tensors: arguments are validated once, every later
+    ``forward()`` / ``backward()`` goes straight to the C ABI with the stored pointers.
+
+    The checked Python entry points cost about 20 us of host time per call; with a collective in the step
+    that makes the host, not the GPU, the bottleneck.  Binding is for training loops that reuse their buffers
+    (the tensors must stay alive and keep their storage while the object is used).
+    """
+
+    def __init__(self, feats, weights, grad_out, out, in_grad, w_grad, kpos, imap, omap, arch80: bool, group=None):
+        import torch
+        from . import _lib, backend
+        k_vol = backend._common(feats, weights, kpos, imap, omap)
+        backend._check_feat("out", out, feats.dtype)
+        backend._check_feat("grad_out", grad_out, feats.dtype)
+        backend._check_feat("in_grad", in_grad, feats.dtype)
+        backend._check_feat("w_grad", w_grad, feats.dtype, dim=3)
+        if in_grad.shape != feats.shape or w_grad.shape != weights.shape or out.shape != grad_out.shape \
+                or out.size(1) != weights.size(2):
+            raise ValueError("output / gradient buffers do not match the shapes of feats, weights and grad_out")
+        self._keep = (feats, weights, grad_out, out, in_grad, w_grad, kpos, imap, omap)
+        self._L, self._check, self.group = _lib.lib, _lib.check, group
+        self.device = feats.device
+        self.fp16 = feats.dtype == torch.float16
+        dtype, math = backend._dtype_math(feats, arch80)
+        self.multi = world_size(group) > 1
+        n_in, n_out, c_in, c_out = feats.size(0), out.size(0), weights.size(1), weights.size(2)
+        p = lambda t: t.data_ptr() if t.numel() > 0 else None
+        self._fwd_args = (p(feats), p(weights), p(out), p(kpos), None, p(imap), p(omap), n_in, n_out, c_in, c_in, c_out,
+                          k_vol, 0, dtype, math, 0)
+        self._dgrad_args = (p(grad_out), p(weights), p(in_grad), p(kpos), p(imap), p(omap), n_in, n_out, c_in, c_out, k_vol,
+                            dtype, math)
+        self.w_grad, self.part, ws_ptr, ws_bytes, accumulate = w_grad, None, None, 0, 1
+        if self.fp16 and (self.multi or backend.kernel_family("wgrad", c_in, c_out, feats.dtype, arch80) != "tcgen05"):
+            ws = backend.wgrad_workspace(c_in, c_out, k_vol, feats.device)
+            ws_ptr, ws_bytes = ws.data_ptr(), ws.numel() * 4
+            if self.multi:
+                self.part, accumulate = ws[: w_grad.numel()], 0  # fp32 sums, all-reduced, then added to w_grad
+        elif not self.fp16 and self.multi:
+            self.part = torch.zeros_like(w_grad)                   # fp32 storage: sums of this rank, all-reduced, then added
+        target = self.part if (self.part is not None and not self.fp16) else w_grad
+        self._wgrad_args = (p(feats), p(grad_out), p(target), p(kpos), p(imap), p(omap), n_in, n_out, c_in, c_out, k_vol,
+                            dtype, math, ws_ptr, ws_bytes, accumulate)
+
+    def _stream(self):
+        import torch
+        return torch.cuda.current_stream(self.device).cuda_stream
+
+    def forward(self):
+        self._check(self._L.fgms_b200_fusion_fwd(*self._fwd_args, self._stream()))
+
+    def backward(self):
+        """wgrad first, its all-reduce beside dgrad, then the sums are added to ``w_grad``."""
+        import torch.distributed as dist
+        st = self._stream()
+        if self.part is not None and not self.fp16:
+            self.part.zero_()
+        self._check(self._L.fgms_b200_wgrad(*self._wgrad_args, st))
+        work = dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group, async_op=True) if self.multi else None
+        self._check(self._L.fgms_b200_dgrad(*self._dgrad_args, st))
+        if work is not None:
+            work.wait()
+            if self.fp16:
+                self._check(self._L.fgms_b200_wgrad_finalize(self.w_grad.data_ptr(), self.part.data_ptr(), self.w_grad.numel(), st))
+            else:
+                self.w_grad += self.part
