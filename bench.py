@@ -163,7 +163,7 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
-        # the 1.8 MB weight-gradient all-reduce is latency-bound; on this pool's 8-GPU boxes it was measured
+        # the 1.8 MB weight-gradient all-reduce is latency-bound; on 8-GPU B200 boxes it was measured
         # faster without NVLink-switch reductions (30.8 vs 46.0 us back to back, 213 vs 228 us per step)
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     if world != args.gpus:
@@ -241,7 +241,7 @@ def run_ours(args):
     # the kernels, their order and their arguments are those of the eager step.  --no-graph times the eager step.
     graph = None
     launches_per_step = None
-    if args.graph and world == 1:  # with a collective in the step, capture hung on this pool: N > 1 runs the bound plan eagerly
+    if args.graph and world == 1:  # with a collective in the step the capture hung when it was tried with 2 ranks: N > 1 runs the bound step eagerly
         try:
             c0 = backend.launch_count()
             g = torch.cuda.CUDAGraph()
