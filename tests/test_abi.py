@@ -73,6 +73,31 @@ def test_workspace_size_and_family_queries():
     assert L.fgms_b200_kernel_family(0, 128, 128, _lib.DTYPE_F32, _lib.MATH_FP32) == 0  # fp32 math is never tensor-core
     assert L.fgms_b200_kernel_family(0, 17, 33, _lib.DTYPE_F16, _lib.MATH_F16) == 0
     assert L.fgms_b200_launch_count() >= 0
+    # tensor-core shapes: whole 128-byte spans, at most 256 channels; the weight gradient tiles fewer row counts
+    F16, F32, M16, TF = _lib.DTYPE_F16, _lib.DTYPE_F32, _lib.MATH_F16, _lib.MATH_TF32
+    fam = lambda ci, co, dt, m: [L.fgms_b200_kernel_family(ps, ci, co, dt, m) for ps in range(3)]
+    assert fam(128, 128, F16, M16) == [1, 1, 1]
+    assert fam(256, 256, F16, M16) == [1, 1, 1]
+    assert fam(64, 192, F16, M16) == [1, 1, 1]
+    assert fam(192, 64, F16, M16) == [1, 1, 0]      # 192 gradient rows are not tiled
+    assert fam(32, 64, F32, TF) == [1, 1, 1]
+    assert fam(96, 32, F32, TF) == [1, 1, 0]
+    assert fam(32, 32, F16, M16) == [0, 0, 0]       # 64-byte rows
+    assert fam(320, 64, F16, M16) == [0, 0, 0]      # more than 256 channels
+    assert L.fgms_b200_kernel_family(3, 64, 64, F16, M16) < 0
+    # map-builder workspace: grows with both the table and the dense [k_vol x columns] scratch
+    w = L.fgms_b200_map_workspace_bytes
+    assert w(0, 0, 27) > 0 and w(1000, 1000, 27) < w(2000, 1000, 27) < w(2000, 2000, 27) and w(1000, 1000, 27) % 256 == 0
+    assert w(-1, 10, 27) == 0 and w(10, 10, 0) == 0
+
+
+def test_map_builders_validate_without_a_device():
+    L = _lib.lib
+    assert L.fgms_b200_build_submanifold_map(None, 10, 4, None, None, None, None, 0, None, None) == _lib.ERR_INVALID_ARG  # even kernel
+    assert L.fgms_b200_build_submanifold_map(None, -1, 3, None, None, None, None, 0, None, None) == _lib.ERR_INVALID_ARG
+    assert L.fgms_b200_build_strided_map(None, 10, 1, None, None, None, None, None, 0, None, None) == _lib.ERR_INVALID_ARG  # stride < 2
+    assert L.fgms_b200_transpose_map(None, None, None, 5, 0, 0, None, None, None, None, 0, None) == _lib.ERR_INVALID_ARG
+    assert _lib.last_error()
 
 
 def test_seq_forward_checks_host_counts():
