@@ -99,43 +99,7 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint32_t bar) {
 // make generic-proxy / cp.async writes to shared memory visible to the async proxy (tcgen05.mma)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
-// ------------------------------------------------------------------ bulk (TMA engine) reduction smem -> global
-// dst[0..bytes) += src[0..bytes) element-wise, performed asynchronously by the copy engine.  Both
-// addresses 16-byte aligned, bytes a multiple of 16.  The calling thread tracks completion with its
-// own bulk groups.
-template <bool F32>
-__device__ __forceinline__ void bulk_reduce_add(void* dst_global, uint32_t src_smem, uint32_t bytes) {
-  if (F32) {
-    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(dst_global),
-                 "r"(src_smem), "r"(bytes)
-                 : "memory");
-  } else {
-    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.noftz.f16 [%0], [%1], %2;" ::"l"(dst_global),
-                 "r"(src_smem), "r"(bytes)
-                 : "memory");
-  }
-}
-__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
-// wait until at most N of this thread's bulk groups still have to READ their shared-memory source
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void bulk_wait() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
-}
-
 // ------------------------------------------------------------------ tcgen05
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
 // whole warp; ncols a power of two in [32, 512]; the base address lands in *smem_dst
 __device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols)
