@@ -1,12 +1,12 @@
 #!/usr/bin/env python
-"""Benchmark of the sparse-convolution hot path: one layer, forward + dgrad + wgrad per step.
+"""Benchmark of the sparse-convolution hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload cfg4] [--impl ours|reference]
 
-A *step* is one forward and one backward (input gradient + weight gradient) of one layer over one
-synthetic voxel cloud (``fgms_b200.workloads``; default ``cfg4``: LiDAR-like sweep, 3x3x3
-submanifold, fp16 128->128 — the configuration the 60 %-of-roofline target is stated on).  The metric
-is effective TFLOPS = 6 * pairs * c_in * c_out / time; ``ms_per_step`` is ms per layer.
+Headline: one layer, forward + dgrad + wgrad per step, over one synthetic voxel cloud
+(``fgms_b200.workloads``; default ``cfg4``: LiDAR-like sweep, 3x3x3 submanifold, fp16 128->128 — the
+configuration the 60 %-of-roofline target is stated on).  The metric is effective TFLOPS =
+6 * pairs * c_in * c_out / time; ``ms_per_step`` is ms per layer.
 
 * ``value``      device-resident inputs, CUDA events around each step on the launching stream, L2
                  flushed (a 512 MB buffer is overwritten) and outputs re-zeroed before every step,
@@ -15,15 +15,21 @@ is effective TFLOPS = 6 * pairs * c_in * c_out / time; ``ms_per_step`` is ms per
                  copies of features, weights, output gradient and maps, the three operator calls,
                  and device -> host copies of all three results, all inside the timed interval.
 * ``roofline``   for the slowest of the three kernels of the step: algorithmic bytes of that pass
-                 divided by its mean launch duration (events recorded around the call, in the same
-                 timed steps), against the measured HBM copy bandwidth.
+                 divided by its mean launch duration (events around the kernel call alone, no
+                 collective inside), against max(bytes / measured HBM bandwidth, flops / tensor peak).
 * ``cpu_baseline`` / ``--impl reference``  the reference's CPU definition (cpu-check.py /
                  cpu-check-back.py) restated per offset as index_select -> matmul -> index_add_ in
                  fp32 on all host threads (``oracle/spconv_oracle.py``), on the same workload.
+* ``cfg5``       beside the headline: one training step of the MinkUNet-style stack
+                 (``fgms_b200.unet``, 25 layers, fp16), one ~120 k-voxel scene per rank, with the
+                 bucketed weight-gradient all-reduce overlapped with the backward when N > 1.
 
 With N > 1 (torchrun, one rank per GPU) every rank holds its own scene of the same kind (weak
 scaling, data parallel); the weight-gradient partial sums are combined with one NCCL all-reduce
-inside the timed step.  Rank 0 prints ONE JSON line.
+inside the timed step, and the exchanged result is checked on the GPUs after the timed loop
+(``multi_gpu_check``).  ``--shard rows`` instead cuts ONE scene over the ranks by output-row range
+(forward) / input-row range (dgrad) and reports that step as ``strong_scaling``.
+Rank 0 prints ONE JSON line.
 """
 from __future__ import annotations
 
@@ -41,19 +47,27 @@ sys.path.insert(0, ROOT)
 METRIC = "spconv fwd+bwd effective TFLOPS (6*pairs*c_in*c_out / time), one layer"
 UNIT = "TFLOPS"
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (kernel -> workload -> bytes); None where no capture exists yet.
-NCU_TRAFFIC = {  # profiles/cfg4_fp16_c128_umma_kernels.md
+# dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the named pass on the named workload, from
+# ncu captures of this benchmark's own command; reported only for exactly that pass and workload.
+NCU_TRAFFIC = {
     ("fwd", "cfg4"): 79.8e6, ("dgrad", "cfg4"): 79.4e6, ("wgrad", "cfg4"): 83.7e6,
 }
 
 
 def load_peaks():
+    """(HBM GB/s, dense 16-bit tensor TFLOPS, source).  tf32 runs at half the 16-bit tensor rate."""
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
         with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
+            d = json.load(f)
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+def tensor_peak_tflops(mode: str, f16_peak: float):
+    """Peak of the arithmetic a mode runs on: fp16 = the measured dense 16-bit figure, tf32 = half of it (the
+    tensor cores' tf32 rate), fp32 = the CUDA cores' FFMA rate (148 SMs x 128 lanes x 2 flop x 1.965 GHz)."""
+    return {"fp16": f16_peak, "tf32": f16_peak / 2, "fp32": 148 * 128 * 2 * 1.965e9 / 1e12}[mode]
 
 
 class ClockSampler:
@@ -118,6 +132,47 @@ def cpu_step(wl, threads: int):
     return time.perf_counter() - t0
 
 
+def cpu_literal_cfg1():
+    """The reference's own nested loops (cpu-check.py:16-44, cpu-check-back.py:16-44) timed on cfg1, the one
+    configuration they can finish: the C restatement of the loops on the whole layer, and the Python form on
+    the first 300 pairs scaled to the layer's pair count."""
+    import numpy as np
+    from fgms_b200 import clouds, workloads
+    from oracle import c_oracle
+    from oracle import spconv_oracle as orc
+    wl = workloads.get("cfg1")
+    km = wl.kmap
+    f, w, g = clouds.make_tensors(km.n_in, km.n_out, wl.c_in, wl.c_out, km.k_vol, wl.seed, np.float32)
+    c_oracle.fwd(f, w, km.n_out, km.knnz, km.imap, km.omap, acc="f32")
+    t0 = time.perf_counter()
+    c_oracle.fwd(f, w, km.n_out, km.knnz, km.imap, km.omap, acc="f32")
+    c_oracle.bwd(g, w, f, km.n_in, km.knnz, km.imap, km.omap, acc="f32")
+    c_ms = (time.perf_counter() - t0) * 1e3
+    sample = 300
+    knnz = np.zeros_like(km.knnz)
+    knnz[0] = sample  # the loops only count pairs per offset; which offset they sit in does not change the work
+    t0 = time.perf_counter()
+    orc.fwd_literal(f, w, km.n_out, knnz, km.imap, km.omap, False)
+    orc.bwd_literal(g, w, f, km.n_in, knnz, km.imap, km.omap)
+    py_ms = (time.perf_counter() - t0) * 1e3 * km.pairs / sample
+    return {"workload": "cfg1 (8000 voxels, 14040 pairs, fp32 16->16), fwd + dgrad + wgrad", "cores": 1,
+            "c_loops_ms": c_ms, "python_loops_ms_extrapolated": py_ms,
+            "sample": f"C: whole layer; Python: first {sample} pairs, scaled by pairs / {sample}"}
+
+
+def workload_config(wl, gpus, shard):
+    """Identical in both arms for one command line: what is computed, not how it is timed."""
+    km = wl.kmap
+    if gpus == 1:
+        par = "single GPU"
+    elif shard == "rows":
+        par = f"one scene cut over {gpus} GPUs by output / input row range, wgrad all-reduce"
+    else:
+        par = f"dp{gpus} (one scene per GPU, wgrad all-reduce)"
+    return {"workload": f"{wl.name}: {wl.description}", "n_in": km.n_in, "n_out": km.n_out, "pairs": km.pairs,
+            "k_vol": km.k_vol, "c_in": wl.c_in, "c_out": wl.c_out, "math": wl.mode, "seed": wl.seed, "parallelism": par}
+
+
 def run_reference(args):
     """The reference's CPU path timed on the host cores; rank 0 only."""
     if int(os.environ.get("RANK", "0")) != 0:
@@ -126,30 +181,247 @@ def run_reference(args):
     wl = workloads.get(args.workload)
     threads = os.cpu_count() or 1
     flops = workloads.flops(wl)
-    for _ in range(max(1, min(args.warmup, 1))):
+    for _ in range(args.warmup):
         cpu_step(wl, threads)
-    times = [cpu_step(wl, threads) for _ in range(max(1, min(args.steps, 5)))]
+    times = [cpu_step(wl, threads) for _ in range(args.steps)]
     t = statistics.mean(times)
     val = flops / t / 1e12
     line = {
-        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
-        "warmup": 1, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "impl": "reference", "metric": METRIC, "value": val, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": workload_config(wl, args.gpus, "host memory"),
+        "config": workload_config(wl, args.gpus, args.shard),
         "cpu_baseline": {"value": val, "unit": UNIT, "cores": threads, "kind": "port",
-                         "sample": f"whole {wl.name} layer, fwd+dgrad+wgrad, mean of {len(times)} runs"},
+                         "sample": f"whole {wl.name} layer, fwd+dgrad+wgrad, per step; mean of {len(times)} steps"},
         "e2e": {"value": val, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "timing": "host wall clock around each step, inputs in host memory",
     }
     print(json.dumps(line), flush=True)
 
 
-def workload_config(wl, gpus, l2):
+# ---------------------------------------------------------------------------------------------
+# cfg5: the encoder-decoder stack
+# ---------------------------------------------------------------------------------------------
+def run_cfg5(args, dev, rank, world, flush):
+    """One training step of the stack per timed step; one scene per rank.  Returns rank 0's report (None elsewhere)."""
+    import torch
+    import torch.distributed as dist
+    from fgms_b200 import backend, unet, workloads
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def build(scenes, first):
+        wl = workloads.unet_workload(scenes=scenes, first_scene=first)
+        spec = unet.minkunet_spec(wl.c_in, wl.widths)
+        umaps = unet.build_unet_maps(torch.from_numpy(wl.coords).to(dev))
+        weights = unet.unet_weights(spec, umaps, wl.seed)
+        feats, grad_out = torch.from_numpy(wl.feats).to(dev), torch.from_numpy(wl.grad_out).to(dev)
+        return wl, spec, umaps, weights, feats, grad_out
+
+    def time_steps(run, steps, warm):
+        for _ in range(warm):
+            flush(); run()
+        barrier()
+        evs = []
+        for _ in range(steps):
+            flush()
+            a, b = ev(), ev()
+            a.record(); run(); b.record()
+            evs.append((a, b))
+        barrier()
+        return sum(a.elapsed_time(b) for a, b in evs)
+
+    steps = max(3, min(args.steps, args.cfg5_steps))
+    wl, spec, umaps, weights, feats, grad_out = build(1, rank)
+    step = unet.UNetStep(spec, umaps, weights, feats, grad_out)
+    flops_local = unet.step_flops(spec, umaps)
+    run = step.run
+    graph = None
+    if world == 1 and args.graph:
+        # no collective in the single-rank step: capture its launches once, replay them
+        for _ in range(2):
+            step.run()
+        torch.cuda.synchronize()
+        try:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                step.run()
+            graph, run = g, g.replay
+        except Exception as exc:
+            sys.stderr.write(f"bench: cfg5 CUDA graph capture failed ({exc!r}); timing eager launches\n")
+            torch.cuda.synchronize()
+    total_ms = time_steps(run, steps, 3)
+    report = {"what": wl.description, "layers": len(spec), "steps": steps,
+              "launch": "CUDA-graph replay" if graph is not None else "eager launches",
+              "kernels_per_step": step.launches_per_step}
+
+    check = None
+    exposed_ms = None
+    if world > 1:
+        # the same step without the collectives: what the all-reduces add to the step is their exposed time
+        alone = unet.UNetStep(spec, umaps, weights, feats, grad_out, exchange=False)
+        alone_ms = time_steps(alone.run, steps, 2)
+        # result check: the all-reduced gradient equals the sum of the ranks' own gradients
+        step.run(); alone.run()
+        torch.cuda.synchronize()
+        mine = alone.w_grad.float()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        ref = torch.stack(parts).sum(0)
+        scale = float(ref.abs().max())
+        werr = float((step.w_grad.float() - ref).abs().max()) / max(scale, 1e-30)
+        oerr = float((step.val[spec[-1].dst].float() - alone.val[spec[-1].dst].float()).abs().max())
+        check = {"wgrad_rel_err": werr, "out_abs_diff_vs_single_rank": oerr, "ok": bool(werr <= 1e-2)}
+
+    stats = torch.tensor([total_ms, flops_local, (alone_ms if world > 1 else 0.0), float(umaps.voxels[0])],
+                         dtype=torch.float64, device=dev)
+    if world > 1:
+        mx = stats.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
+        sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
+        total_ms, flops_all, alone_ms = float(mx[0]), float(sm[1]), float(mx[2])
+        exposed_ms = (total_ms - alone_ms) / steps
+        oks = torch.tensor([1.0 if check["ok"] else 0.0], device=dev)
+        dist.all_reduce(oks, op=dist.ReduceOp.MIN)
+        check["ok"] = bool(oks.item() > 0)
+    else:
+        flops_all = flops_local
+    if not rank == 0:
+        return None, check
+    report.update({"ms_per_step": total_ms / steps, "value": flops_all * steps / (total_ms * 1e-3) / 1e12, "unit": UNIT,
+                   "scaling": "weak (one scene per rank)", "voxels_per_level": umaps.voxels,
+                   "flops_per_step_all_ranks": flops_all})
+    if world > 1:
+        report["allreduce"] = {"buckets": len(step.buckets), "bytes_fp32": int(step.w_grad.numel() * 4),
+                               "exposed_ms_per_step": exposed_ms, "kernels_only_ms_per_step": alone_ms / steps}
+        report["multi_gpu_check"] = check
+    else:
+        # per-layer table and the roofline of the slowest call (eager launches with events around every call)
+        hbm, f16_peak, _ = load_peaks()
+        rows = step.profile(reps=5, flush=flush)
+        by_name = {l.name: (i, l) for i, l in enumerate(spec)}
+        table, worst = [], None
+        for r in rows:
+            i, l = by_name[r["layer"]]
+            pairs = int(umaps.of(l).pairs)
+            b = workloads.layer_bytes(pairs, l.c_in, l.c_out, l.k_vol, 2, r["pass"])
+            fl = 2.0 * pairs * l.c_in * l.c_out
+            t_roof = max(b / (hbm * 1e9), fl / (f16_peak * 1e12)) * 1e3
+            fam = backend.kernel_family(r["pass"], l.c_in, l.c_out, torch.float16, True, l.k_vol)
+            row = {"layer": l.name, "pass": r["pass"], "shape": f"{l.c_in}->{l.c_out} k{l.k_vol}", "pairs": pairs,
+                   "ms": round(r["ms"], 5), "frac": round(t_roof / r["ms"], 4), "family": fam}
+            table.append(row)
+            if worst is None or r["ms"] > worst[0]["ms"]:
+                worst = (row, b)
+        report["per_call"] = table
+        report["sum_of_calls_ms"] = sum(r["ms"] for r in rows)
+        w, b = worst
+        report["slowest_call"] = {"layer": w["layer"], "pass": w["pass"], "shape": w["shape"], "ms": w["ms"],
+                                  "achieved_gbs": b / (w["ms"] * 1e-3) / 1e9, "peak_gbs": hbm, "frac": w["frac"]}
+        del step, graph
+        # the whole batch of 8 scenes on this one GPU (what the single-GPU case of the configuration is)
+        try:
+            wl8, spec8, umaps8, weights8, feats8, grad8 = build(8, 0)
+            step8 = unet.UNetStep(spec8, umaps8, weights8, feats8, grad8)
+            run8 = step8.run
+            if args.graph:
+                for _ in range(2):
+                    step8.run()
+                torch.cuda.synchronize()
+                g8 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g8):
+                    step8.run()
+                run8 = g8.replay
+            n8 = max(3, steps // 2)
+            ms8 = time_steps(run8, n8, 2)
+            report["batch8_one_gpu"] = {"voxels_per_level": umaps8.voxels, "ms_per_step": ms8 / n8,
+                                        "value": unet.step_flops(spec8, umaps8) * n8 / (ms8 * 1e-3) / 1e12, "unit": UNIT}
+        except Exception as exc:  # reported, not fatal: the headline does not depend on it
+            report["batch8_one_gpu"] = {"error": repr(exc)}
+    return report, check
+
+
+# ---------------------------------------------------------------------------------------------
+# one scene cut over the ranks by row range
+# ---------------------------------------------------------------------------------------------
+def run_row_shard(args, dev, rank, world, wl, p, flush):
+    """Forward on this rank's output-row range, dgrad on its input-row range, wgrad on the forward cut's pairs with
+    the partial sums all-reduced.  The maps are cut on the device (``dist.shard_map_device``).  Checks that rows
+    outside the rank's range stay exactly zero and that the gathered result matches the uncut run."""
+    import torch
+    import torch.distributed as dist
+    from fgms_b200 import backend
+    from fgms_b200 import dist as fdist
+
+    ev = lambda: torch.cuda.Event(enable_timing=True)
     km = wl.kmap
-    return {"workload": f"{wl.name}: {wl.description}", "n_in": km.n_in, "n_out": km.n_out, "pairs": km.pairs,
-            "k_vol": km.k_vol, "c_in": wl.c_in, "c_out": wl.c_out, "math": wl.mode, "seed": wl.seed,
-            "parallelism": f"dp{gpus} (one scene per GPU, wgrad all-reduce)" if gpus > 1 else "single GPU",
-            "l2": l2}
+    out_cut = fdist.shard_map_device(p.kpos, p.imap, p.omap, km.n_out, rank, world, by="out")
+    in_cut = fdist.shard_map_device(p.kpos, p.imap, p.omap, km.n_in, rank, world, by="in")
+    out = torch.zeros((km.n_out, wl.c_out), dtype=p.dtype, device=dev)
+    in_grad = torch.zeros((km.n_in, wl.c_in), dtype=p.dtype, device=dev)
+    w_grad = torch.zeros_like(p.weights)
+    part = torch.zeros(p.weights.numel(), dtype=torch.float32, device=dev)
+
+    def step():
+        backend.fgms_fusion_fwd_cuda(p.feats, p.weights, 0, out, out_cut.kpos, None, out_cut.imap, out_cut.omap, False, p.arch80)
+        if p.dtype == torch.float16:
+            backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, out_cut.kpos, out_cut.imap, out_cut.omap, p.arch80,
+                                    workspace=part, accumulate=False)
+        else:
+            part.zero_()
+            backend.fgms_wgrad_cuda(p.feats, p.grad_out, part.view_as(w_grad), out_cut.kpos, out_cut.imap, out_cut.omap, p.arch80)
+        work = dist.all_reduce(part, async_op=True)
+        backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, in_cut.kpos, in_cut.imap, in_cut.omap, p.arch80)
+        work.wait()
+        if p.dtype == torch.float16:
+            backend.wgrad_finalize(w_grad, part)
+        else:
+            w_grad.add_(part.view_as(w_grad))
+
+    def prepare():
+        out.zero_(); in_grad.zero_(); w_grad.zero_(); flush()
+
+    for _ in range(args.warmup):
+        prepare(); step()
+    dist.barrier(); torch.cuda.synchronize()
+    evs = []
+    steps = min(args.steps, 100)
+    for _ in range(steps):
+        prepare()
+        a, b = ev(), ev()
+        a.record(); step(); b.record()
+        evs.append((a, b))
+    dist.barrier(); torch.cuda.synchronize()
+    ms = sum(a.elapsed_time(b) for a, b in evs) / steps
+    # ---- checks
+    prepare(); step(); torch.cuda.synchronize()
+    lo, hi = out_cut.row_range
+    outside_zero = bool((out[:lo] == 0).all() and (out[hi:] == 0).all())
+    ilo, ihi = in_cut.row_range
+    outside_zero = outside_zero and bool((in_grad[:ilo] == 0).all() and (in_grad[ihi:] == 0).all())
+    full_out = out.clone(); dist.all_reduce(full_out)          # the ranges are disjoint: the sum is the concatenation
+    full_in = in_grad.clone(); dist.all_reduce(full_in)
+    ref_out = torch.zeros_like(out); ref_in = torch.zeros_like(in_grad); ref_w = torch.zeros_like(w_grad)
+    backend.fgms_fusion_fwd_cuda(p.feats, p.weights, 0, ref_out, p.kpos, None, p.imap, p.omap, False, p.arch80)
+    backend.fgms_bwd_cuda(p.grad_out, p.feats, p.weights, 0, ref_in, ref_w, p.kpos, None, p.imap, p.omap, False, p.arch80)
+    rel = lambda a, b: float((a.float() - b.float()).abs().max()) / max(float(b.float().abs().max()), 1e-30)
+    errs = {"out": rel(full_out, ref_out), "in_grad": rel(full_in, ref_in), "w_grad": rel(w_grad, ref_w)}
+    pairs_local = torch.tensor([float(out_cut.imap.numel()), float(in_cut.imap.numel()), ms], dtype=torch.float64, device=dev)
+    gathered = [torch.empty_like(pairs_local) for _ in range(world)]
+    dist.all_gather(gathered, pairs_local)
+    ok = outside_zero and max(errs.values()) <= 1e-2
+    flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+    ms_max = max(float(g[2]) for g in gathered)
+    return {"mode": "one scene, forward by output-row range, dgrad by input-row range, wgrad partial sums all-reduced",
+            "ms_per_step": ms_max, "value": 6.0 * km.pairs * wl.c_in * wl.c_out / (ms_max * 1e-3) / 1e12, "unit": UNIT,
+            "pairs_per_rank_fwd": [int(g[0]) for g in gathered], "pairs_per_rank_dgrad": [int(g[1]) for g in gathered],
+            "rows_outside_own_range_zero": outside_zero, "rel_err_vs_uncut": errs, "ok": bool(flag.item() > 0)}
 
 
 def run_ours(args):
@@ -163,8 +435,8 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     if world > 1:
-        # the 1.8 MB weight-gradient all-reduce is latency-bound; on 8-GPU B200 boxes it was measured
-        # faster without NVLink-switch reductions (30.8 vs 46.0 us back to back, 213 vs 228 us per step)
+        # the weight-gradient all-reduces are small and latency-bound; on 8-GPU B200 boxes they were measured
+        # faster without NVLink-switch reductions (30.8 vs 46.0 us back to back for 1.8 MB)
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torchrun --nproc-per-node {args.gpus}")
@@ -174,7 +446,8 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    wl = workloads.get(args.workload, seed_offset=1000 * rank)
+    shard_rows = args.shard == "rows" and world > 1
+    wl = workloads.get(args.workload, seed_offset=0 if shard_rows else 1000 * rank)
     km = wl.kmap
     p = workloads.LayerTensors(km, wl.c_in, wl.c_out, wl.seed, wl.mode, device=dev)
     layer = SceneParallelLayer(p.kpos, p.imap, p.omap, p.qsum, p.arch80)
@@ -182,50 +455,44 @@ def run_ours(args):
     in_grad = torch.zeros((km.n_in, wl.c_in), dtype=p.dtype, device=dev)
     w_grad = torch.zeros_like(p.weights)
     flush_buf = torch.empty(512 << 20, dtype=torch.uint8, device=dev)
+    flush = lambda: flush_buf.fill_(1)  # evict L2 (126 MB) so that every step starts cold
 
     def prepare():
         out.zero_(); in_grad.zero_(); w_grad.zero_()
-        flush_buf.fill_(1)  # evict L2 (126 MB) so that every step starts cold
+        flush()
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
     pass_ms = {"fwd": [], "dgrad": [], "wgrad": []}
 
     bound = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80) if world > 1 else None
+    bound_alone = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80,
+                                  exchange=False) if world > 1 else None
+    ws = backend.wgrad_workspace(wl.c_in, wl.c_out, km.k_vol, dev) if p.dtype == torch.float16 else None
+    part32 = torch.zeros_like(w_grad) if p.dtype != torch.float16 else None
 
-    def layer_wgrad():
+    def wgrad_kernel_only():
+        """The weight-gradient kernel of this step's form, without the collective (for the per-pass times)."""
         if p.dtype == torch.float16 and world == 1:
             backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80)
         elif p.dtype == torch.float16:
-            ws = backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80,
-                                         workspace=backend.wgrad_workspace(wl.c_in, wl.c_out, km.k_vol, dev), accumulate=False)
-            part = ws[: w_grad.numel()]
-            dist.all_reduce(part)
-            backend.wgrad_finalize(w_grad, part)
+            backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80, workspace=ws, accumulate=False)
         else:
-            part = torch.zeros_like(w_grad)
-            backend.fgms_wgrad_cuda(p.feats, p.grad_out, part, p.kpos, p.imap, p.omap, p.arch80)
-            if world > 1:
-                dist.all_reduce(part)
-            w_grad.add_(part)
+            backend.fgms_wgrad_cuda(p.feats, p.grad_out, part32 if world > 1 else w_grad, p.kpos, p.imap, p.omap, p.arch80)
 
-    def step(record, passes=False):
-        """One fwd + dgrad + wgrad.  record: events around the step; passes: also between the passes (used in a
-        separate loop only, so that the headline step has nothing between its kernels)."""
-        e = [ev() for _ in range(4)] if record else None
+    def step(record, which=bound):
+        """One fwd + dgrad + wgrad; nothing between the launches.  record: events around the step."""
+        e = [ev(), ev()] if record else None
         if record: e[0].record()
-        if world > 1 and not passes:
+        if world > 1:
             # data parallel: the step bound to its buffers (no per-call argument checks on the host); wgrad first,
             # its all-reduce runs beside dgrad
-            bound.forward()
-            bound.backward()
-            if record: e[3].record()
-            return e
-        layer.forward(p.feats, p.weights, out)
-        if passes: e[1].record()
-        backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
-        if passes: e[2].record()
-        layer_wgrad()
-        if record: e[3].record()
+            which.forward()
+            which.backward()
+        else:
+            layer.forward(p.feats, p.weights, out)
+            backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
+            wgrad_kernel_only()
+        if record: e[1].record()
         return e
 
     def barrier():
@@ -237,11 +504,12 @@ def run_ours(args):
     for _ in range(args.warmup):
         prepare(); step(False)
     barrier()
-    # The same launches are captured once into a CUDA graph and replayed, which takes the host out of the step;
-    # the kernels, their order and their arguments are those of the eager step.  --no-graph times the eager step.
+    # With one rank the launches are captured once into a CUDA graph and replayed, which takes the host out of
+    # the step; the kernels, their order and their arguments are those of the eager step.  --no-graph times the
+    # eager step.  With a collective in the step the launches stay eager.
     graph = None
     launches_per_step = None
-    if args.graph and world == 1:  # with a collective in the step the capture hung when it was tried with 2 ranks: N > 1 runs the bound step eagerly
+    if args.graph and world == 1:
         try:
             c0 = backend.launch_count()
             g = torch.cuda.CUDAGraph()
@@ -260,11 +528,12 @@ def run_ours(args):
     def timed_step():
         if graph is None:
             return step(True)
-        e = [ev() for _ in range(4)]
-        e[0].record(); graph.replay(); e[3].record()
+        e = [ev(), ev()]
+        e[0].record(); graph.replay(); e[1].record()
         return e
 
     launches0 = backend.launch_count()
+    fallbacks0 = backend.fallback_count()
     events = []
     with ClockSampler(local) as clocks:
         for _ in range(args.steps):
@@ -272,16 +541,33 @@ def run_ours(args):
             events.append(timed_step())
         barrier()
     launches = (backend.launch_count() - launches0) if graph is None else launches_per_step * args.steps
-    step_ms = [e[0].elapsed_time(e[3]) for e in events]
-    total_ms = sum(step_ms)
+    total_ms = sum(e[0].elapsed_time(e[1]) for e in events)
 
-    # per-pass durations (for the roofline of the slowest pass): same steps with events between the passes
-    pass_events = []
+    # the same step without the collective (N > 1): the difference is the all-reduce's exposed time
+    alone_ms = 0.0
+    if world > 1:
+        evs = []
+        for _ in range(min(args.steps, 50)):
+            prepare()
+            evs.append(step(True, bound_alone))
+        barrier()
+        alone_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+
+    # per-pass durations (for the roofline of the slowest pass): kernels alone, events between the passes
+    pe = []
     for _ in range(min(args.steps, 50)):
         prepare()
-        pass_events.append(step(True, passes=True))
+        e = [ev() for _ in range(4)]
+        e[0].record()
+        layer.forward(p.feats, p.weights, out)
+        e[1].record()
+        backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
+        e[2].record()
+        wgrad_kernel_only()
+        e[3].record()
+        pe.append(e)
     barrier()
-    for e in pass_events:
+    for e in pe:
         pass_ms["fwd"].append(e[0].elapsed_time(e[1]))
         pass_ms["dgrad"].append(e[1].elapsed_time(e[2]))
         pass_ms["wgrad"].append(e[2].elapsed_time(e[3]))
@@ -293,10 +579,37 @@ def run_ours(args):
     warm = []
     for _ in range(args.steps):
         out.zero_(); in_grad.zero_(); w_grad.zero_()
-        e = timed_step()
-        warm.append(e)
+        warm.append(timed_step())
     barrier()
-    warm_ms = sum(e[0].elapsed_time(e[3]) for e in warm)
+    warm_ms = sum(e[0].elapsed_time(e[1]) for e in warm)
+
+    # ---- multi-GPU result check: the exchanged weight gradient is the sum of the ranks' own sums ----------
+    check = None
+    if world > 1:
+        out.zero_(); in_grad.zero_(); w_grad.zero_()
+        bound.forward(); bound.backward()
+        torch.cuda.synchronize()
+        got_w, got_out, got_in = w_grad.clone(), out.clone(), in_grad.clone()
+        if p.dtype == torch.float16:
+            backend.fgms_wgrad_cuda(p.feats, p.grad_out, w_grad, p.kpos, p.imap, p.omap, p.arch80, workspace=ws, accumulate=False)
+            mine = ws[: w_grad.numel()].clone()
+        else:
+            mine = torch.zeros_like(w_grad)
+            backend.fgms_wgrad_cuda(p.feats, p.grad_out, mine, p.kpos, p.imap, p.omap, p.arch80)
+            mine = mine.flatten()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        ref_w = torch.stack(parts).sum(0)
+        ref_out = torch.zeros_like(out); ref_in = torch.zeros_like(in_grad)
+        layer.forward(p.feats, p.weights, ref_out)
+        backend.fgms_dgrad_cuda(p.grad_out, p.weights, ref_in, p.kpos, p.imap, p.omap, p.arch80)
+        rel = lambda a, b: float((a.float().flatten() - b.float().flatten()).abs().max()) / max(float(b.float().abs().max()), 1e-30)
+        check = {"wgrad_rel_err": rel(got_w, ref_w), "out_rel_err": rel(got_out, ref_out), "in_grad_rel_err": rel(got_in, ref_in)}
+        ok = max(check.values()) <= 1e-2
+        flag = torch.tensor([1.0 if ok else 0.0], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        check["ok"] = bool(flag.item() > 0)
+        check["what"] = "all-reduced w_grad vs the sum of every rank's own fp32 sums (all_gather); out / in_grad vs the single-rank entry points"
 
     # ---- end to end with host buffers ----------------------------------------------------------
     # Three streams and two sets of device / host buffers: the upload of step i + 1 and the download of
@@ -336,21 +649,23 @@ def run_ours(args):
                 h_out[b][k].copy_(d_out[b][k], non_blocking=True)
             ev_down[b].record(s_down)
 
+    e2e_steps = min(args.steps, 100)
     for i in range(max(2, args.warmup // 2) * 2):
         e2e_step(i)
     barrier()
     e2e_t0, e2e_t1 = ev(), [ev() for _ in range(3)]
     e2e_t0.record(s_up)
     s_run.wait_event(e2e_t0); s_down.wait_event(e2e_t0)
-    for i in range(args.steps):
+    for i in range(e2e_steps):
         e2e_step(i)
     for e, st in zip(e2e_t1, (s_up, s_run, s_down)):
         e.record(st)
     barrier()
-    e2e_ms = max(e2e_t0.elapsed_time(e) for e in e2e_t1)
+    e2e_ms = max(e2e_t0.elapsed_time(e) for e in e2e_t1) / e2e_steps
     # the last step's results, downloaded through the same path, must match the device-resident run
     # (fp16 reds arrive in a different order every run, so the comparison allows rounding differences)
-    if not torch.allclose(h_out[(args.steps - 1) & 1]["out"].float(), out.cpu().float(), rtol=2e-2, atol=2e-2):
+    out.zero_(); layer.forward(p.feats, p.weights, out); torch.cuda.synchronize()
+    if not torch.allclose(h_out[(e2e_steps - 1) & 1]["out"].float(), out.cpu().float(), rtol=2e-2, atol=2e-2):
         raise SystemExit("end-to-end forward output differs from the device-resident run")
 
     # ---- the step before the path: this scene's kernel map built on the device (reported beside the headline)
@@ -363,7 +678,7 @@ def run_ours(args):
         torch.cuda.synchronize()
         evs = []
         for _ in range(10):
-            flush_buf.fill_(1)
+            flush()
             a, b = ev(), ev()
             a.record(); dk = gpu_maps.build_submanifold_map(coords_d, 3); b.record()
             evs.append((a, b))
@@ -375,49 +690,74 @@ def run_ours(args):
                        "identical_to_host_builder": same,
                        "note": "includes the allocation of its outputs and one stream synchronisation (pair count)"}
 
+    fallbacks = backend.fallback_count() - fallbacks0
+    strong = run_row_shard(args, dev, rank, world, wl, p, flush) if shard_rows else None
+    cfg5, cfg5_check = (None, None)
+    if args.cfg5:
+        del d_in, d_out
+        cfg5, cfg5_check = run_cfg5(args, dev, rank, world, flush)
+
     # ---- reduce over ranks ---------------------------------------------------------------------
     flops_local = workloads.flops(wl)
-    stats = torch.tensor([total_ms, warm_ms, e2e_ms, flops_local, float(km.pairs)], dtype=torch.float64, device=dev)
+    stats = torch.tensor([total_ms, warm_ms, e2e_ms, flops_local, float(km.pairs), alone_ms], dtype=torch.float64, device=dev)
     if world > 1:
         mx = stats.clone(); dist.all_reduce(mx, op=dist.ReduceOp.MAX)
         sm = stats.clone(); dist.all_reduce(sm, op=dist.ReduceOp.SUM)
-        total_ms, warm_ms, e2e_ms = float(mx[0]), float(mx[1]), float(mx[2])
+        total_ms, warm_ms, e2e_ms, alone_ms = float(mx[0]), float(mx[1]), float(mx[2]), float(mx[5])
         flops_all, pairs_all = float(sm[3]), float(sm[4])
     else:
         flops_all, pairs_all = flops_local, float(km.pairs)
 
+    failed = [n for n, c in (("multi_gpu_check", check), ("cfg5.multi_gpu_check", cfg5_check), ("strong_scaling", strong))
+              if c is not None and not c["ok"]]
     if rank == 0:
         k = args.steps
         value = flops_all * k / (total_ms * 1e-3) / 1e12
+        hbm, f16_peak, peak_src = load_peaks()
+        t_peak = tensor_peak_tflops(wl.mode, f16_peak)
+        pass_flops = 2.0 * km.pairs * wl.c_in * wl.c_out
         dom = max(pass_ms, key=lambda n: statistics.mean(pass_ms[n]))
         dom_ms = statistics.mean(pass_ms[dom])
         dom_bytes = workloads.algorithmic_bytes(wl, dom)
-        peak, peak_src = load_peaks()
+        t_hbm, t_tensor = dom_bytes / (hbm * 1e9), pass_flops / (t_peak * 1e12)
         achieved = dom_bytes / (dom_ms * 1e-3) / 1e9
         all_bytes = workloads.algorithmic_bytes(wl, "all")
+        t_roof_step = max(all_bytes / (hbm * 1e9), 3 * pass_flops / (t_peak * 1e12)) * 1e3
+        family = backend.kernel_family(dom, wl.c_in, wl.c_out, p.dtype, p.arch80, km.k_vol)
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": k, "warmup": args.warmup,
             "ms_per_step": total_ms / k, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
             "dtype": {"fp16": "f16 (fp32 accumulate)", "tf32": "tf32 (fp32 accumulate)", "fp32": "f32"}[wl.mode],
             "data": "synthetic",
-            "config": dict(workload_config(wl, world, "flushed before every step (512 MB overwrite), outputs re-zeroed, both untimed"),
-                           launch="CUDA-graph replay of the step's launches" if graph is not None else "eager launches"),
-            "e2e": {"value": flops_all * k / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
-                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms / k},
+            "config": workload_config(wl, world, args.shard),
+            "timing": {"l2": "flushed before every step (512 MB overwrite), outputs re-zeroed, both untimed",
+                       "launch": "CUDA-graph replay of the step's launches" if graph is not None else "eager launches"},
+            "e2e": {"value": flops_all / (e2e_ms * 1e-3) / 1e12, "unit": UNIT, "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
             "gpu_launches": int(launches),
+            "tensor_core_fallbacks": int(fallbacks),
             "clocks": clocks.summary(),
-            "roofline": {"bound": "hbm", "kernel": f"{dom} ({backend.kernel_family(dom, wl.c_in, wl.c_out, p.dtype, p.arch80)})",
-                         "achieved": achieved, "peak": peak, "peak_source": peak_src, "unit": "GB/s",
-                         "frac": achieved / peak, "traffic": NCU_TRAFFIC.get((dom, wl.name)),
-                         "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms},
-            "step_roofline": {"algorithmic_bytes": all_bytes, "t_roof_ms": all_bytes / (peak * 1e9) * 1e3,
-                              "frac": all_bytes / (peak * 1e9) * 1e3 / (total_ms / k)},
+            "roofline": {"bound": "hbm" if t_hbm >= t_tensor else "tensor", "kernel": f"{dom} ({family})",
+                         "achieved": achieved, "peak": hbm, "peak_source": peak_src, "unit": "GB/s",
+                         "frac": max(t_hbm, t_tensor) / (dom_ms * 1e-3), "traffic": NCU_TRAFFIC.get((dom, wl.name)),
+                         "algorithmic_bytes_per_launch": dom_bytes, "ms_per_launch": dom_ms,
+                         "t_hbm_ms": t_hbm * 1e3, "t_tensor_ms": t_tensor * 1e3, "tensor_peak_tflops": t_peak},
+            "step_roofline": {"algorithmic_bytes": all_bytes, "t_roof_ms": t_roof_step, "frac": t_roof_step / (total_ms / k)},
             "pass_ms": {n: statistics.mean(v) for n, v in pass_ms.items()},
             "value_l2_warm": flops_all * k / (warm_ms * 1e-3) / 1e12,
             "ms_per_step_l2_warm": warm_ms / k,
             "pairs_all_ranks": pairs_all,
             "map_builder": map_builder,
         }
+        if world > 1:
+            line["pass_ms"]["wgrad_kernel"] = line["pass_ms"]["wgrad"]
+            line["pass_ms"]["step_kernels_only"] = alone_ms
+            line["pass_ms"]["allreduce_exposed"] = total_ms / k - alone_ms
+            line["multi_gpu_check"] = check
+        if strong is not None:
+            line["strong_scaling"] = strong
+        if cfg5 is not None:
+            line["cfg5"] = cfg5
         if world == 1 and not args.no_cpu:
             threads = os.cpu_count() or 1
             cpu_step(wl, threads)
@@ -425,9 +765,14 @@ def run_ours(args):
             line["cpu_baseline"] = {"value": flops_local / min(ts) / 1e12, "unit": UNIT, "cores": threads, "kind": "port",
                                     "sample": f"whole {wl.name} layer (fwd+dgrad+wgrad) on the host, best of 3",
                                     "ms_per_step": min(ts) * 1e3}
+            line["cpu_literal_cfg1"] = cpu_literal_cfg1()
+        if failed:
+            line["failed_checks"] = failed
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if failed:
+        raise SystemExit(f"result check failed: {failed}")
 
 
 def main():
@@ -437,11 +782,17 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="cfg4")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--shard", default="scenes", choices=["scenes", "rows"],
+                    help="N > 1: 'scenes' = one scene per rank (weak scaling); 'rows' also cuts one scene by row range and reports strong_scaling")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the eager step instead of a CUDA-graph replay of it")
+    ap.add_argument("--no-cfg5", dest="cfg5", action="store_false", help="skip the encoder-decoder stack")
+    ap.add_argument("--cfg5-steps", type=int, default=20)
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
+    if args.steps < 1:
+        args.steps = 1
     if args.impl == "reference":
         run_reference(args)
     else:

@@ -19,14 +19,14 @@ MATH_FP32, MATH_TF32, MATH_F16 = 0, 1, 2
 
 # name -> (restype, argtypes); mirrors include/fgms_b200.h declaration by declaration
 SIGNATURES = {
-    "fgms_b200_fusion_fwd": (c_int, [c_void_p] * 7 + [c_int] * 6 + [c_int64] + [c_int] * 3 + [c_void_p]),
-    "fgms_b200_seq_fwd": (c_int, [c_void_p] * 7 + [c_int] * 6 + [c_int64] + [c_int] * 3 + [c_void_p]),
-    "fgms_b200_dgrad": (c_int, [c_void_p] * 6 + [c_int] * 7 + [c_void_p]),
-    "fgms_b200_wgrad": (c_int, [c_void_p] * 6 + [c_int] * 7 + [c_void_p, c_size_t, c_int, c_void_p]),
+    "fgms_b200_fusion_fwd": (c_int, [c_void_p] * 7 + [c_int64] + [c_int] * 6 + [c_int64] + [c_int] * 3 + [c_void_p]),
+    "fgms_b200_seq_fwd": (c_int, [c_void_p] * 7 + [c_int64] + [c_int] * 6 + [c_int64] + [c_int] * 3 + [c_void_p]),
+    "fgms_b200_dgrad": (c_int, [c_void_p] * 6 + [c_int64] + [c_int] * 7 + [c_void_p]),
+    "fgms_b200_wgrad": (c_int, [c_void_p] * 6 + [c_int64] + [c_int] * 7 + [c_void_p, c_size_t, c_int, c_void_p]),
     "fgms_b200_wgrad_finalize": (c_int, [c_void_p, c_void_p, c_int64, c_void_p]),
-    "fgms_b200_wgrad_f16_noalloc": (c_int, [c_void_p] * 6 + [c_int] * 6 + [c_void_p]),
+    "fgms_b200_wgrad_f16_noalloc": (c_int, [c_void_p] * 6 + [c_int64] + [c_int] * 6 + [c_void_p]),
     "fgms_b200_wgrad_workspace_bytes": (c_size_t, [c_int] * 4),
-    "fgms_b200_bwd": (c_int, [c_void_p] * 9 + [c_int] * 6 + [c_int64] + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
+    "fgms_b200_bwd": (c_int, [c_void_p] * 9 + [c_int64] + [c_int] * 6 + [c_int64] + [c_int] * 3 + [c_void_p, c_size_t, c_void_p]),
     "fgms_b200_map_workspace_bytes": (c_size_t, [c_int] * 3),
     "fgms_b200_build_submanifold_map": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_size_t,
                                                 c_void_p, c_void_p]),
@@ -34,7 +34,8 @@ SIGNATURES = {
                                             c_size_t, c_void_p, c_void_p]),
     "fgms_b200_transpose_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_size_t, c_void_p]),
-    "fgms_b200_kernel_family": (c_int, [c_int] * 5),
+    "fgms_b200_kernel_family": (c_int, [c_int] * 6),
+    "fgms_b200_fallback_count": (c_int64, []),
     "fgms_b200_device_status": (c_int64, [c_int]),
     "fgms_b200_launch_count": (c_int64, []),
     "fgms_b200_last_error": (c_char_p, []),

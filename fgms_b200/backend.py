@@ -25,7 +25,8 @@ import torch
 from . import _lib
 
 __all__ = ["fgms_fusion_fwd_cuda", "fgms_fwd_cuda", "fgms_bwd_cuda", "fgms_dgrad_cuda", "fgms_wgrad_cuda",
-           "wgrad_workspace", "wgrad_finalize", "fgms_wgrad_noalloc_cuda", "kernel_family", "device_status", "launch_count"]
+           "wgrad_workspace", "wgrad_finalize", "fgms_wgrad_noalloc_cuda", "kernel_family", "fallback_count",
+           "device_status", "launch_count"]
 
 _L = _lib.lib
 
@@ -114,8 +115,8 @@ def fgms_fusion_fwd_cuda(in_feats, kernel, sum_nnz, out_feats, kpos, qkpos, in_m
     with torch.cuda.device(in_feats.device):
         _lib.check(_L.fgms_b200_fusion_fwd(
             _ptr(in_feats), _ptr(kernel), _ptr(out_feats), _ptr(kpos), _ptr(qkpos), _ptr(in_map), _ptr(out_map),
-            in_feats.size(0), out_feats.size(0), in_feats.size(1), kernel.size(1), kernel.size(2), k_vol,
-            int(sum_nnz), dtype, math, int(bool(separate_mid)), _stream()))
+            in_map.numel(), in_feats.size(0), out_feats.size(0), in_feats.size(1), kernel.size(1), kernel.size(2),
+            k_vol, int(sum_nnz), dtype, math, int(bool(separate_mid)), _stream()))
 
 
 def fgms_fwd_cuda(in_feats, kernel, sum_nnz, out_feats, kernel_nnz, kernel_pos, in_map, out_map,
@@ -131,8 +132,8 @@ def fgms_fwd_cuda(in_feats, kernel, sum_nnz, out_feats, kernel_nnz, kernel_pos, 
     with torch.cuda.device(in_feats.device):
         _lib.check(_L.fgms_b200_seq_fwd(
             _ptr(in_feats), _ptr(kernel), _ptr(out_feats), kernel_nnz.data_ptr(), _ptr(kernel_pos), _ptr(in_map),
-            _ptr(out_map), in_feats.size(0), out_feats.size(0), in_feats.size(1), kernel.size(1), kernel.size(2),
-            k_vol, int(sum_nnz), dtype, math, int(bool(separate_mid)), _stream()))
+            _ptr(out_map), in_map.numel(), in_feats.size(0), out_feats.size(0), in_feats.size(1), kernel.size(1),
+            kernel.size(2), k_vol, int(sum_nnz), dtype, math, int(bool(separate_mid)), _stream()))
 
 
 def fgms_bwd_cuda(out_feats_grad, in_feats, kernel, sum_nnz, in_feats_grad, kernel_grad, kpos, qkpos,
@@ -150,13 +151,13 @@ def fgms_bwd_cuda(out_feats_grad, in_feats, kernel, sum_nnz, in_feats_grad, kern
             raise ValueError("out_feats_grad width differs from the kernel's output channels")
     dtype, math = _dtype_math(in_feats, arch80)
     ws = None
-    if dtype == _lib.DTYPE_F16 and not _single_launch_wgrad(kernel.size(1), kernel.size(2), in_feats.dtype, arch80, None):
+    if dtype == _lib.DTYPE_F16 and not _single_launch_wgrad(kernel.size(1), kernel.size(2), k_vol, in_feats.dtype, arch80, None):
         ws = wgrad_workspace(kernel.size(1), kernel.size(2), k_vol, in_feats.device)
     with torch.cuda.device(in_feats.device):
         _lib.check(_L.fgms_b200_bwd(
             _ptr(out_feats_grad), _ptr(in_feats), _ptr(kernel), _ptr(in_feats_grad), _ptr(kernel_grad), _ptr(kpos),
-            _ptr(qkpos), _ptr(in_map), _ptr(out_map), in_feats.size(0), out_feats_grad.size(0), in_feats.size(1),
-            kernel.size(1), kernel.size(2), k_vol, int(sum_nnz), dtype, math, int(bool(separate_mid)),
+            _ptr(qkpos), _ptr(in_map), _ptr(out_map), in_map.numel(), in_feats.size(0), out_feats_grad.size(0),
+            in_feats.size(1), kernel.size(1), kernel.size(2), k_vol, int(sum_nnz), dtype, math, int(bool(separate_mid)),
             _ptr(ws), ws.numel() * 4 if ws is not None else 0, _stream()))
 
 
@@ -168,8 +169,8 @@ def fgms_dgrad_cuda(out_feats_grad, kernel, in_feats_grad, kpos, in_map, out_map
     with torch.cuda.device(kernel.device):
         _lib.check(_L.fgms_b200_dgrad(
             _ptr(out_feats_grad), _ptr(kernel), _ptr(in_feats_grad), _ptr(kpos), _ptr(in_map), _ptr(out_map),
-            in_feats_grad.size(0), out_feats_grad.size(0), kernel.size(1), kernel.size(2), k_vol, dtype, math,
-            _stream()))
+            in_map.numel(), in_feats_grad.size(0), out_feats_grad.size(0), kernel.size(1), kernel.size(2), k_vol,
+            dtype, math, _stream()))
 
 
 # fp16 weight gradients: False = single launch, every CTA adds its fp32 partial sums (rounded to fp16) into
@@ -178,9 +179,9 @@ def fgms_dgrad_cuda(out_feats_grad, kernel, in_feats_grad, kpos, in_map, out_map
 WGRAD_FP32_SUMS = False
 
 
-def _single_launch_wgrad(c_in, c_out, dtype, arch80, fp32_sums) -> bool:
+def _single_launch_wgrad(c_in, c_out, k_vol, dtype, arch80, fp32_sums) -> bool:
     want_fp32 = WGRAD_FP32_SUMS if fp32_sums is None else fp32_sums
-    return dtype == torch.float16 and not want_fp32 and kernel_family("wgrad", c_in, c_out, dtype, arch80) == "tcgen05"
+    return dtype == torch.float16 and not want_fp32 and kernel_family("wgrad", c_in, c_out, dtype, arch80, k_vol) == "tcgen05"
 
 
 def fgms_wgrad_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map, out_map, arch80,
@@ -197,16 +198,18 @@ def fgms_wgrad_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map, out_map
     _check_index("kpos", kpos, in_feats.device, k_vol + 1)
     _check_index("in_map", in_map, in_feats.device)
     _check_index("out_map", out_map, in_feats.device)
+    if in_map.numel() != out_map.numel():
+        raise ValueError("in_map and out_map differ in length")
     dtype, math = _dtype_math(in_feats, arch80)
-    single = workspace is None and accumulate and _single_launch_wgrad(kernel_grad.size(1), kernel_grad.size(2),
+    single = workspace is None and accumulate and _single_launch_wgrad(kernel_grad.size(1), kernel_grad.size(2), k_vol,
                                                                        in_feats.dtype, arch80, fp32_sums)
     if dtype == _lib.DTYPE_F16 and workspace is None and not single:
         workspace = wgrad_workspace(kernel_grad.size(1), kernel_grad.size(2), k_vol, in_feats.device)
     with torch.cuda.device(in_feats.device):
         _lib.check(_L.fgms_b200_wgrad(
             _ptr(in_feats), _ptr(out_feats_grad), _ptr(kernel_grad), _ptr(kpos), _ptr(in_map), _ptr(out_map),
-            in_feats.size(0), out_feats_grad.size(0), kernel_grad.size(1), kernel_grad.size(2), k_vol, dtype, math,
-            _ptr(workspace), workspace.numel() * 4 if workspace is not None else 0, int(bool(accumulate)),
+            in_map.numel(), in_feats.size(0), out_feats_grad.size(0), kernel_grad.size(1), kernel_grad.size(2), k_vol,
+            dtype, math, _ptr(workspace), workspace.numel() * 4 if workspace is not None else 0, int(bool(accumulate)),
             _stream()))
     return workspace
 
@@ -230,12 +233,14 @@ def fgms_wgrad_noalloc_cuda(in_feats, out_feats_grad, kernel_grad, kpos, in_map,
     _check_index("kpos", kpos, in_feats.device, k_vol + 1)
     _check_index("in_map", in_map, in_feats.device)
     _check_index("out_map", out_map, in_feats.device)
+    if in_map.numel() != out_map.numel():
+        raise ValueError("in_map and out_map differ in length")
     _, math = _dtype_math(in_feats, arch80)
     with torch.cuda.device(in_feats.device):
         _lib.check(_L.fgms_b200_wgrad_f16_noalloc(
             _ptr(in_feats), _ptr(out_feats_grad), _ptr(kernel_grad), _ptr(kpos), _ptr(in_map), _ptr(out_map),
-            in_feats.size(0), out_feats_grad.size(0), kernel_grad.size(1), kernel_grad.size(2), k_vol, math,
-            _stream()))
+            in_map.numel(), in_feats.size(0), out_feats_grad.size(0), kernel_grad.size(1), kernel_grad.size(2), k_vol,
+            math, _stream()))
 
 
 def wgrad_finalize(kernel_grad: torch.Tensor, partial_f32: torch.Tensor) -> None:
@@ -250,12 +255,22 @@ def wgrad_finalize(kernel_grad: torch.Tensor, partial_f32: torch.Tensor) -> None
         _lib.check(_L.fgms_b200_wgrad_finalize(_ptr(kernel_grad), _ptr(partial_f32), kernel_grad.numel(), _stream()))
 
 
-def kernel_family(pass_: str, c_in: int, c_out: int, dtype: torch.dtype, arch80: bool = True) -> str:
-    """``"tcgen05"`` or ``"simt"``: which kernel family the dispatch uses for a shape."""
+def kernel_family(pass_: str, c_in: int, c_out: int, dtype: torch.dtype, arch80: bool = True, k_vol: int = 27) -> str:
+    """``"tcgen05"`` or ``"simt"``: which kernel family the dispatch uses for a shape (channel counts that are
+    multiples of 16 up to 256 whose operands fit shared memory run on tcgen05 unless ``arch80`` is false for
+    fp32 storage)."""
     d = _lib.DTYPE_F16 if dtype == torch.float16 else _lib.DTYPE_F32
     m = _lib.MATH_F16 if dtype == torch.float16 else (_lib.MATH_TF32 if arch80 else _lib.MATH_FP32)
-    fam = _L.fgms_b200_kernel_family({"fwd": 0, "dgrad": 1, "wgrad": 2}[pass_], c_in, c_out, d, m)
+    fam = _L.fgms_b200_kernel_family({"fwd": 0, "dgrad": 1, "wgrad": 2}[pass_], c_in, c_out, k_vol, d, m)
+    if fam < 0:
+        _lib.check(fam)
     return "tcgen05" if fam == 1 else "simt"
+
+
+def fallback_count() -> int:
+    """Launches that should have run on tcgen05 by their shape but ran on the CUDA-core kernels because a
+    tensor was not 16-byte aligned (0 in a healthy run)."""
+    return int(_L.fgms_b200_fallback_count())
 
 
 def device_status(reset: bool = True) -> int:

@@ -24,6 +24,7 @@ struct GmsParams {
   const int32_t* kpos;         // [k_vol + 1]
   const int32_t* gather_map;   // [pairs]
   const int32_t* scatter_map;  // [pairs]
+  int pairs;                   // entries the two maps hold: no position >= pairs is ever read
   int n_gather, n_scatter;
   int k_dim, n_dim;            // contraction width, output width
   int c_in, c_out;             // layout of `weights`
@@ -39,6 +40,7 @@ struct WgradParams {
   const int32_t* kpos;
   const int32_t* in_map;
   const int32_t* out_map;
+  int pairs;  // entries the two maps hold
   int n_in, n_out, c_in, c_out, k_vol;
   // fp16 storage, tensor-core kernel only: add every CTA's fp32 partial sums, rounded to fp16, straight
   // into the fp16 gradient (dw is then unused)
@@ -53,11 +55,23 @@ struct WgradParams {
 // and searching the padded prefix sums per block (backend/utils.cuh:6-27).  Here each CTA derives
 // the table from the unpadded `kpos` itself, so no padded rows are ever scheduled.
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void build_tile_table(int TILE, const int32_t* __restrict__ kpos, int k_vol,
-                                                 int dense_rows, int* tile_start /* [k_vol+2] */) {
+// `kpos` comes from the caller's device memory and is not trusted: every entry is clamped to
+// [0, pairs] (pairs = length of the maps) on its way into shared memory, so a stale or mismatched
+// kpos can shorten segments but never moves a map read past the end of the maps.  A clamped entry
+// is counted as a problem once per launch.
+__device__ __forceinline__ void build_tile_table(int TILE, const int32_t* __restrict__ kpos, int pairs, int k_vol,
+                                                 int dense_rows, int* kpos_s /* [k_vol+1] */,
+                                                 int* tile_start /* [k_vol+2] */) {
+  for (int s = threadIdx.x; s <= k_vol; s += blockDim.x) {
+    const int v = __ldg(kpos + s);
+    const int c = min(max(v, 0), pairs);
+    if (v != c && blockIdx.x == 0) report_problem();
+    kpos_s[s] = c;
+  }
+  __syncthreads();
   // counts first (parallel), then the first warp turns them into running sums, 32 segments at a time
   for (int s = threadIdx.x; s <= k_vol; s += blockDim.x) {
-    int cnt = (s < k_vol) ? (__ldg(kpos + s + 1) - __ldg(kpos + s)) : dense_rows;
+    int cnt = (s < k_vol) ? (kpos_s[s + 1] - kpos_s[s]) : dense_rows;
     if (cnt < 0) cnt = 0;
     tile_start[s + 1] = (cnt + TILE - 1) / TILE;
   }
@@ -115,23 +129,28 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
   __half2 h = __floats2half2_rn(a, b);
   return *reinterpret_cast<uint32_t*>(&h);
 }
-__device__ __forceinline__ void red_add_h2(__half* p, float a, float b) {
-  uint32_t v = pack_half2(a, b);
-  asm volatile("red.global.add.noftz.f16x2 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ void red_add_h8(__half* p, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("red.global.add.noftz.v4.f16x2 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(a), "r"(b), "r"(c),
                "r"(d)
                : "memory");
 }
 
-// Add v[0..n) to consecutive elements starting at p.  `vec` says that p is suitably aligned
-// (16 bytes for float4, 4 bytes for half2) — decided once per launch from the channel count.
+__device__ __forceinline__ void red_add_h4(__half* p, uint32_t a, uint32_t b) {
+  asm volatile("red.global.add.noftz.v2.f16x2 [%0], {%1, %2};" ::"l"(p), "r"(a), "r"(b) : "memory");
+}
+
+// Add v[0..n) to consecutive elements starting at p.  `vec` says that p is suitably aligned for one
+// vector red of N elements (16 bytes for four floats, 8 bytes for four halves) — decided once per
+// launch from the channel count and the base address.
 template <int N>
 __device__ __forceinline__ void scatter_add(float* p, const float (&v)[N], int valid, bool vec) {
-  if (N == 4 && vec && valid == 4) {
-    red_add_v4(p, v[0], v[1], v[2], v[3]);
-  } else {
+  if constexpr (N == 4) {
+    if (vec && valid == 4) {
+      red_add_v4(p, v[0], v[1], v[2], v[3]);
+      return;
+    }
+  }
+  {
 #pragma unroll
     for (int c = 0; c < N; ++c)
       if (c < valid) red_add(p + c, v[c]);
@@ -139,13 +158,13 @@ __device__ __forceinline__ void scatter_add(float* p, const float (&v)[N], int v
 }
 template <int N>
 __device__ __forceinline__ void scatter_add(__half* p, const float (&v)[N], int valid, bool vec) {
-  if (N % 2 == 0 && vec) {
-#pragma unroll
-    for (int c = 0; c < N; c += 2) {
-      if (c + 1 < valid) red_add_h2(p + c, v[c], v[c + 1]);
-      else if (c < valid) red_add(p + c, v[c]);
+  if constexpr (N == 4) {
+    if (vec && valid == 4) {
+      red_add_h4(p, pack_half2(v[0], v[1]), pack_half2(v[2], v[3]));
+      return;
     }
-  } else {
+  }
+  {
 #pragma unroll
     for (int c = 0; c < N; ++c)
       if (c < valid) red_add(p + c, v[c]);

@@ -14,15 +14,16 @@
 #include "common.cuh"
 #include "simt_kernels.cuh"
 #include "map_builder.cuh"
-#ifndef FGMS_NO_UMMA
 #include "umma_gms3.cuh"
 #include "umma_wgrad3.cuh"
-#endif
 
 namespace {
 
 thread_local char g_err[512] = "";
 std::atomic<long long> g_launches{0};
+// launches that the shape alone would have sent to the tensor-core kernels but that ran on the CUDA-core
+// kernels (base pointers not 16-byte aligned): fgms_b200_fallback_count()
+std::atomic<long long> g_fallbacks{0};
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -83,36 +84,30 @@ int check_dims(int n_in, int n_out, int c_in, int c_out, int k_vol) {
   return FGMS_OK;
 }
 
-// tcgen05 kernels cover rows that are whole 128-byte swizzle spans on both sides
-bool umma_shape_ok(int c_in, int c_out, int dtype) {
-#ifdef FGMS_NO_UMMA
-  (void)c_in; (void)c_out; (void)dtype;
-  return false;
-#else
-  return fgms::umma_supported(c_in, c_out, dtype == FGMS_DTYPE_F16 ? 2 : 4);
-#endif
+// Which family a pass of a shape runs on.  One decision for the dispatch and for fgms_b200_kernel_family:
+// the tensor-core kernels' own plans (shape rules and shared-memory fit for this k_vol on this device).
+bool plan_gms(bool trans, int c_in, int c_out, int k_vol, int dtype, int math, int max_smem) {
+  if (math == FGMS_MATH_FP32) return false;
+  fgms::G3Config cfg;
+  return fgms::g3_plan(c_in, c_out, dtype == FGMS_DTYPE_F16 ? 2 : 4, k_vol, max_smem, trans, &cfg);
 }
-
-bool use_umma(int c_in, int c_out, int dtype, int math) {
-  return math != FGMS_MATH_FP32 && umma_shape_ok(c_in, c_out, dtype);
-}
-
-// the weight-gradient kernel tiles fewer row counts than forward / dgrad (c_in a multiple of 128, or 64, or one
-// 128-byte span); the shared-memory size used for the check is the opt-in maximum of sm_100
-bool use_umma_wgrad(int c_in, int c_out, int dtype, int math) {
-#ifdef FGMS_NO_UMMA
-  return false;
-#else
-  if (!use_umma(c_in, c_out, dtype, math)) return false;
+bool plan_wgrad(int c_in, int c_out, int k_vol, int dtype, int math, int max_smem) {
+  if (math == FGMS_MATH_FP32) return false;
   fgms::W3Config cfg;
-  return fgms::w3_config(c_in, c_out, dtype == FGMS_DTYPE_F16 ? 2 : 4, 232448, 27, fgms::W3_MAX_PB, &cfg);
-#endif
+  return fgms::w3_plan(c_in, c_out, dtype == FGMS_DTYPE_F16 ? 2 : 4, k_vol, max_smem, &cfg);
+}
+
+// upper bound on the tiles of `tile` pairs a map of `pairs` entries in k_vol (+1 dense) segments can have
+int simt_grid(long long pairs, int dense_rows, int k_vol, int tile, int sms) {
+  const long long bound = (pairs + dense_rows) / tile + k_vol + 1;
+  const long long full = (long long)sms * 4;
+  return (int)(bound < full ? (bound < 1 ? 1 : bound) : full);
 }
 
 template <typename T, bool TRANS>
 int launch_simt_gms(const fgms::GmsParams& p, cudaStream_t st, int sms) {
-  const size_t dyn = (size_t)(p.k_vol + 2) * sizeof(int);
-  const int grid = sms * 4;
+  const size_t dyn = (size_t)(2 * p.k_vol + 3) * sizeof(int);
+  const int grid = simt_grid(p.pairs, p.dense_rows, p.k_vol, fgms::SIMT_TILE_M, sms);
   if (p.n_dim <= 16) fgms::simt_gms_kernel<T, TRANS, 1><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
   else fgms::simt_gms_kernel<T, TRANS, 4><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
   return check_launch("simt_gms_kernel");
@@ -120,7 +115,7 @@ int launch_simt_gms(const fgms::GmsParams& p, cudaStream_t st, int sms) {
 
 // One gather-GEMM-scatter pass (forward when !trans, dgrad when trans).
 int run_gms(bool trans, const void* src, const void* kernel, void* dst, const int32_t* kpos,
-            const int32_t* gather_map, const int32_t* scatter_map, int n_gather, int n_scatter,
+            const int32_t* gather_map, const int32_t* scatter_map, int64_t map_len, int n_gather, int n_scatter,
             int c_in, int c_out, int k_vol, int dtype, int math, int dense_rows, int dense_weight,
             cudaStream_t st) {
   DeviceInfo di;
@@ -128,19 +123,18 @@ int run_gms(bool trans, const void* src, const void* kernel, void* dst, const in
   fgms::GmsParams p;
   p.src = src; p.weights = kernel; p.dst = dst; p.kpos = kpos;
   p.gather_map = gather_map; p.scatter_map = scatter_map;
+  p.pairs = (int)map_len;
   p.n_gather = n_gather; p.n_scatter = n_scatter;
   p.k_dim = trans ? c_out : c_in;
   p.n_dim = trans ? c_in : c_out;
   p.c_in = c_in; p.c_out = c_out; p.k_vol = k_vol;
   p.dense_rows = dense_rows; p.dense_weight = dense_weight;
-#ifndef FGMS_NO_UMMA
-  if (use_umma(c_in, c_out, dtype, math)) {
+  if (plan_gms(trans, c_in, c_out, k_vol, dtype, math, di.max_smem_optin)) {
     int rc = fgms::launch_umma_gms3(p, trans, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
     if (rc == 0) return check_launch("umma_gms3_kernel");
     if (rc < 0) return fail(FGMS_ERR_CUDA, "umma_gms3_kernel setup failed (%d)", rc);
-    // rc > 0: shape does not fit the tensor-core kernel's shared memory; take the CUDA-core path
+    g_fallbacks.fetch_add(1, std::memory_order_relaxed);  // pointers not 16-byte aligned: CUDA-core path, counted
   }
-#endif
   if (dtype == FGMS_DTYPE_F16)
     return trans ? launch_simt_gms<__half, true>(p, st, di.sms) : launch_simt_gms<__half, false>(p, st, di.sms);
   return trans ? launch_simt_gms<float, true>(p, st, di.sms) : launch_simt_gms<float, false>(p, st, di.sms);
@@ -148,9 +142,17 @@ int run_gms(bool trans, const void* src, const void* kernel, void* dst, const in
 
 int mid_offset(int k_vol) { return (k_vol % 2 == 1) ? k_vol / 2 : 0; }
 
+// `map_len` is the number of entries in_map and out_map hold.  Kernels clamp every kpos entry to it, so no
+// position beyond the maps is read whatever kpos says; maps may be null only when they are empty.
+int check_maps(const int32_t* in_map, const int32_t* out_map, int64_t map_len) {
+  if (map_len < 0 || map_len > 0x7fffffffll) return fail(FGMS_ERR_INVALID_ARG, "map_len %lld outside [0, 2^31)", (long long)map_len);
+  if (map_len > 0 && (!in_map || !out_map)) return fail(FGMS_ERR_INVALID_ARG, "map pointer is null");
+  return FGMS_OK;
+}
+
 int check_fwd_args(const void* in_feats, const void* kernel, void* out_feats, const int32_t* kpos,
-                   const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
-                   int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                   const int32_t* in_map, const int32_t* out_map, int64_t map_len, int n_in, int n_out,
+                   int c_in, int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                    int separate_mid) {
   if (c_in != kernel_c_in)
     return fail(FGMS_ERR_CHANNEL_MISMATCH, "Input feature size and kernel size mismatch");
@@ -159,7 +161,7 @@ int check_fwd_args(const void* in_feats, const void* kernel, void* out_feats, co
   if (!kernel || !kpos) return fail(FGMS_ERR_INVALID_ARG, "kernel / kpos must not be null");
   if ((n_in > 0 && !in_feats) || (n_out > 0 && !out_feats)) return fail(FGMS_ERR_INVALID_ARG, "feature pointer is null");
   if (sum_nnz < 0) return fail(FGMS_ERR_INVALID_ARG, "sum_nnz is negative");
-  if (sum_nnz > 0 && (!in_map || !out_map)) return fail(FGMS_ERR_INVALID_ARG, "map pointer is null");
+  if (int rc = check_maps(in_map, out_map, map_len)) return rc;
   if (separate_mid && n_in != n_out)
     return fail(FGMS_ERR_INVALID_ARG, "separate_mid needs n_in == n_out (got %d, %d)", n_in, n_out);
   return FGMS_OK;
@@ -173,11 +175,11 @@ extern "C" {
 
 int fgms_b200_fusion_fwd(const void* in_feats, const void* kernel, void* out_feats,
                          const int32_t* kpos, const int32_t* qkpos, const int32_t* in_map,
-                         const int32_t* out_map, int n_in, int n_out, int c_in, int kernel_c_in,
-                         int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                         const int32_t* out_map, int64_t map_len, int n_in, int n_out, int c_in,
+                         int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                          int separate_mid, void* stream) {
   (void)qkpos;
-  if (int rc = check_fwd_args(in_feats, kernel, out_feats, kpos, in_map, out_map, n_in, n_out, c_in,
+  if (int rc = check_fwd_args(in_feats, kernel, out_feats, kpos, in_map, out_map, map_len, n_in, n_out, c_in,
                               kernel_c_in, c_out, k_vol, sum_nnz, dtype, math, separate_mid))
     return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
@@ -186,16 +188,16 @@ int fgms_b200_fusion_fwd(const void* in_feats, const void* kernel, void* out_fea
     cudaError_t e = cudaMemsetAsync(out_feats, 0, (size_t)n_out * c_out * elem_size(dtype), st);
     if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
   }
-  return run_gms(false, in_feats, kernel, out_feats, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
+  return run_gms(false, in_feats, kernel, out_feats, kpos, in_map, out_map, map_len, n_in, n_out, c_in, c_out,
                  k_vol, dtype, math, separate_mid ? n_in : 0, mid_offset(k_vol), st);
 }
 
 int fgms_b200_seq_fwd(const void* in_feats, const void* kernel, void* out_feats,
                       const int32_t* kernel_nnz_host, const int32_t* kpos, const int32_t* in_map,
-                      const int32_t* out_map, int n_in, int n_out, int c_in, int kernel_c_in,
-                      int c_out, int k_vol, int64_t sum_nnz, int dtype, int math, int separate_mid,
-                      void* stream) {
-  if (int rc = check_fwd_args(in_feats, kernel, out_feats, kpos, in_map, out_map, n_in, n_out, c_in,
+                      const int32_t* out_map, int64_t map_len, int n_in, int n_out, int c_in,
+                      int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                      int separate_mid, void* stream) {
+  if (int rc = check_fwd_args(in_feats, kernel, out_feats, kpos, in_map, out_map, map_len, n_in, n_out, c_in,
                               kernel_c_in, c_out, k_vol, sum_nnz, dtype, math, separate_mid))
     return rc;
   if (!kernel_nnz_host) return fail(FGMS_ERR_INVALID_ARG, "kernel_nnz (host) must not be null");
@@ -206,19 +208,22 @@ int fgms_b200_seq_fwd(const void* in_feats, const void* kernel, void* out_feats,
   }
   if (total != sum_nnz)
     return fail(FGMS_ERR_INVALID_ARG, "kernel_nnz sums to %lld but sum_nnz is %lld", total, (long long)sum_nnz);
-  return run_gms(false, in_feats, kernel, out_feats, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
+  if (total > map_len)
+    return fail(FGMS_ERR_INVALID_ARG, "kernel_nnz sums to %lld but the maps hold %lld entries", total, (long long)map_len);
+  return run_gms(false, in_feats, kernel, out_feats, kpos, in_map, out_map, map_len, n_in, n_out, c_in, c_out,
                  k_vol, dtype, math, separate_mid ? n_in : 0, mid_offset(k_vol),
                  static_cast<cudaStream_t>(stream));
 }
 
 int fgms_b200_dgrad(const void* out_grad, const void* kernel, void* in_grad, const int32_t* kpos,
-                    const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
-                    int c_out, int k_vol, int dtype, int math, void* stream) {
+                    const int32_t* in_map, const int32_t* out_map, int64_t map_len, int n_in, int n_out,
+                    int c_in, int c_out, int k_vol, int dtype, int math, void* stream) {
   if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
   if (int rc = check_math(dtype, math)) return rc;
   if (!kernel || !kpos) return fail(FGMS_ERR_INVALID_ARG, "kernel / kpos must not be null");
   if ((n_out > 0 && !out_grad) || (n_in > 0 && !in_grad)) return fail(FGMS_ERR_INVALID_ARG, "gradient pointer is null");
-  return run_gms(true, out_grad, kernel, in_grad, kpos, out_map, in_map, n_out, n_in, c_in, c_out, k_vol,
+  if (int rc = check_maps(in_map, out_map, map_len)) return rc;
+  return run_gms(true, out_grad, kernel, in_grad, kpos, out_map, in_map, map_len, n_out, n_in, c_in, c_out, k_vol,
                  dtype, math, 0, 0, static_cast<cudaStream_t>(stream));
 }
 
@@ -239,12 +244,13 @@ int fgms_b200_wgrad_finalize(void* kernel_grad_f16, const void* workspace_f32, i
 }
 
 int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_grad,
-                    const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in,
-                    int n_out, int c_in, int c_out, int k_vol, int dtype, int math, void* workspace,
-                    size_t workspace_bytes, int accumulate_into_kernel_grad, void* stream) {
+                    const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int64_t map_len,
+                    int n_in, int n_out, int c_in, int c_out, int k_vol, int dtype, int math,
+                    void* workspace, size_t workspace_bytes, int accumulate_into_kernel_grad, void* stream) {
   if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
   if (int rc = check_math(dtype, math)) return rc;
   if (!kpos) return fail(FGMS_ERR_INVALID_ARG, "kpos must not be null");
+  if (int rc = check_maps(in_map, out_map, map_len)) return rc;
   if ((n_in > 0 && !in_feats) || (n_out > 0 && !out_grad)) return fail(FGMS_ERR_INVALID_ARG, "feature pointer is null");
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   DeviceInfo di;
@@ -254,8 +260,9 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   float* acc = nullptr;
   // fp16 storage, no workspace: every CTA adds its fp32 partial sums, rounded to fp16, straight into
   // kernel_grad (one launch, no clearing, no second kernel); only the tensor-core kernel does that
+  const bool umma = plan_wgrad(c_in, c_out, k_vol, dtype, math, di.max_smem_optin);
   const bool direct_f16 = dtype == FGMS_DTYPE_F16 && workspace == nullptr && accumulate_into_kernel_grad &&
-                          kernel_grad != nullptr && use_umma_wgrad(c_in, c_out, dtype, math);
+                          kernel_grad != nullptr && umma;
   if (direct_f16) {
     // nothing to prepare
   } else if (dtype == FGMS_DTYPE_F16) {
@@ -277,26 +284,27 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
   fgms::WgradParams p;
   p.feats = in_feats; p.out_grad = out_grad; p.dw = acc; p.kpos = kpos;
   p.in_map = in_map; p.out_map = out_map;
+  p.pairs = (int)map_len;
   p.n_in = n_in; p.n_out = n_out; p.c_in = c_in; p.c_out = c_out; p.k_vol = k_vol;
   if (direct_f16) p.dw_f16 = static_cast<__half*>(kernel_grad);
 
   bool launched = false;
-#ifndef FGMS_NO_UMMA
-  if (use_umma(c_in, c_out, dtype, math)) {
+  if (umma) {
     int rc = fgms::launch_umma_wgrad3(p, dtype == FGMS_DTYPE_F16, st, di.sms, di.max_smem_optin);
     if (rc == 0) {
       if (int rc2 = check_launch("umma_wgrad3_kernel")) return rc2;
       launched = true;
     } else if (rc < 0) {
       return fail(FGMS_ERR_CUDA, "umma_wgrad3_kernel setup failed (%d)", rc);
+    } else if (direct_f16) {
+      return fail(FGMS_ERR_WORKSPACE, "the single-launch fp16 weight gradient needs 16-byte aligned tensors: pass a workspace");
+    } else {
+      g_fallbacks.fetch_add(1, std::memory_order_relaxed);  // pointers not 16-byte aligned: CUDA-core path, counted
     }
   }
-#endif
-  if (!launched && direct_f16)
-    return fail(FGMS_ERR_WORKSPACE, "this shape does not fit the tensor-core weight-gradient kernel: pass a workspace");
   if (!launched) {
-    const size_t dyn = (size_t)(k_vol + 2) * sizeof(int);
-    const int grid = di.sms * 4;
+    const size_t dyn = (size_t)(2 * k_vol + 3) * sizeof(int);
+    const int grid = simt_grid(map_len, 0, k_vol, fgms::SIMT_WG_TILE, di.sms);
     const bool small = c_in <= 16 && c_out <= 16;
     if (dtype == FGMS_DTYPE_F16) {
       if (small) fgms::simt_wgrad_kernel<__half, 1><<<grid, fgms::SIMT_THREADS, dyn, st>>>(p);
@@ -321,60 +329,67 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
 static __device__ __align__(256) float g_noalloc_scratch[FGMS_NOALLOC_MAX_ELEMS];
 
 static int noalloc_scratch(float** out) {
-  static float* cached[64] = {};  // per device ordinal
+  static std::atomic<float*> cached[64];  // per device ordinal; any thread may call
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
   if (dev < 0 || dev >= 64) return fail(FGMS_ERR_CUDA, "device ordinal %d out of range", dev);
-  if (!cached[dev]) {
+  float* addr = cached[dev].load(std::memory_order_acquire);
+  if (!addr) {
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, g_noalloc_scratch);  // `dev` is current: this is ITS copy of the array
     if (e != cudaSuccess || !p) return fail(FGMS_ERR_CUDA, "cudaGetSymbolAddress: %s", cudaGetErrorString(e));
-    cached[dev] = static_cast<float*>(p);
+    addr = static_cast<float*>(p);
+    cached[dev].store(addr, std::memory_order_release);  // two threads racing here store the same address
   }
-  *out = cached[dev];
+  *out = addr;
   return FGMS_OK;
 }
 
 int fgms_b200_wgrad_f16_noalloc(const void* in_feats, const void* out_grad, void* kernel_grad,
                                 const int32_t* kpos, const int32_t* in_map, const int32_t* out_map,
-                                int n_in, int n_out, int c_in, int c_out, int k_vol, int math,
-                                void* stream) {
+                                int64_t map_len, int n_in, int n_out, int c_in, int c_out, int k_vol,
+                                int math, void* stream) {
   if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
   const long long elems = (long long)k_vol * c_in * c_out;
   if (elems > (long long)FGMS_NOALLOC_MAX_ELEMS)
     return fail(FGMS_ERR_WORKSPACE,
                 "k_vol*c_in*c_out = %lld exceeds the %d fp32 values of the built-in scratch array; "
                 "call fgms_b200_wgrad with a workspace instead", elems, (int)FGMS_NOALLOC_MAX_ELEMS);
+  if (int rc = check_maps(in_map, out_map, map_len)) return rc;
   float* scratch = nullptr;
   if (int rc = noalloc_scratch(&scratch)) return rc;
   // fgms_b200_wgrad clears the first `elems` values itself (cudaMemsetAsync on `stream`)
-  return fgms_b200_wgrad(in_feats, out_grad, kernel_grad, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
-                         k_vol, FGMS_DTYPE_F16, math, scratch, (size_t)elems * sizeof(float), 1, stream);
+  return fgms_b200_wgrad(in_feats, out_grad, kernel_grad, kpos, in_map, out_map, map_len, n_in, n_out, c_in,
+                         c_out, k_vol, FGMS_DTYPE_F16, math, scratch, (size_t)elems * sizeof(float), 1, stream);
 }
 
 int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel, void* in_grad,
                   void* kernel_grad, const int32_t* kpos, const int32_t* qkpos,
-                  const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
-                  int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                  const int32_t* in_map, const int32_t* out_map, int64_t map_len, int n_in, int n_out,
+                  int c_in, int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                   int separate_mid, void* workspace, size_t workspace_bytes, void* stream) {
   (void)qkpos; (void)separate_mid;
   if (c_in != kernel_c_in)
     return fail(FGMS_ERR_CHANNEL_MISMATCH, "Input feature size and kernel size mismatch");
   if (sum_nnz < 0) return fail(FGMS_ERR_INVALID_ARG, "sum_nnz is negative");
-  if (sum_nnz > 0 && (!in_map || !out_map)) return fail(FGMS_ERR_INVALID_ARG, "map pointer is null");
-  if (int rc = fgms_b200_dgrad(out_grad, kernel, in_grad, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
-                               k_vol, dtype, math, stream))
+  if (int rc = fgms_b200_dgrad(out_grad, kernel, in_grad, kpos, in_map, out_map, map_len, n_in, n_out, c_in,
+                               c_out, k_vol, dtype, math, stream))
     return rc;
-  return fgms_b200_wgrad(in_feats, out_grad, kernel_grad, kpos, in_map, out_map, n_in, n_out, c_in, c_out,
-                         k_vol, dtype, math, workspace, workspace_bytes, 1, stream);
+  return fgms_b200_wgrad(in_feats, out_grad, kernel_grad, kpos, in_map, out_map, map_len, n_in, n_out, c_in,
+                         c_out, k_vol, dtype, math, workspace, workspace_bytes, 1, stream);
 }
 
-int fgms_b200_kernel_family(int pass, int c_in, int c_out, int dtype, int math) {
-  if (pass < 0 || pass > 2 || !dtype_ok(dtype)) return fail(FGMS_ERR_INVALID_ARG, "bad pass or dtype");
-  if (pass == 2) return use_umma_wgrad(c_in, c_out, dtype, math) ? 1 : 0;
-  return use_umma(c_in, c_out, dtype, math) ? 1 : 0;
+int fgms_b200_kernel_family(int pass, int c_in, int c_out, int k_vol, int dtype, int math) {
+  if (pass < 0 || pass > 2 || !dtype_ok(dtype) || k_vol < 1) return fail(FGMS_ERR_INVALID_ARG, "bad pass, dtype or k_vol");
+  // the current device's opt-in shared memory decides the fit; without a device, that of sm_100 (227 KB)
+  DeviceInfo di;
+  const int max_smem = device_info(&di) == FGMS_OK ? di.max_smem_optin : 232448;
+  if (pass == 2) return plan_wgrad(c_in, c_out, k_vol, dtype, math, max_smem) ? 1 : 0;
+  return plan_gms(pass == 1, c_in, c_out, k_vol, dtype, math, max_smem) ? 1 : 0;
 }
+
+int64_t fgms_b200_fallback_count(void) { return g_fallbacks.load(std::memory_order_relaxed); }
 
 // ---------------------------------------------------------------------------------------------
 // Kernel maps (csrc/map_builder.cuh)
@@ -520,6 +535,6 @@ int64_t fgms_b200_launch_count(void) { return g_launches.load(std::memory_order_
 
 const char* fgms_b200_last_error(void) { return g_err; }
 
-const char* fgms_b200_version(void) { return "fgms_b200 0.1 (sm_100a)"; }
+const char* fgms_b200_version(void) { return "fgms_b200 0.2 (sm_100a)"; }
 
 }  // extern "C"

@@ -4,8 +4,6 @@
 // operand layouts.  All waits are bounded: a wait that runs out returns false and the caller
 // reports it instead of spinning forever.
 #pragma once
-#include <cstdlib>
-
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -200,10 +198,9 @@ __host__ __device__ constexpr uint32_t mnmajor32_offset(uint32_t k, uint32_t byt
 
 }  // namespace umma
 
-// Launch with the programmatic-stream-serialization attribute (environment FGMS_B200_PDL=0: plain launch).
+// Launch with the programmatic-stream-serialization attribute.
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, size_t smem, cudaStream_t st, Args... args) {
-  static const bool pdl = [] { const char* e = getenv("FGMS_B200_PDL"); return !(e && e[0] == '0'); }();
   cudaLaunchConfig_t lc = {};
   lc.gridDim = dim3((unsigned)grid);
   lc.blockDim = dim3((unsigned)block);
@@ -213,7 +210,7 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), int grid, int block, siz
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   lc.attrs = at;
-  lc.numAttrs = pdl ? 1 : 0;
+  lc.numAttrs = 1;
   return cudaLaunchKernelEx(&lc, kernel, static_cast<KArgs>(args)...);
 }
 }  // namespace fgms

@@ -20,14 +20,20 @@
 // no index ring and no patch hand-off.  All waits are bounded; a wait that runs out sets the CTA's
 // abort flag, every role leaves its loop, in-flight copies are awaited and TMEM is freed.
 #pragma once
+#include <atomic>
+
 #include "common.cuh"
 #include "umma.cuh"
 
 namespace fgms {
 
-// shapes the tensor-core kernels take: both channel counts fill whole 128-byte spans, at most 256
+// Shapes the tensor-core kernels take: both channel counts multiples of 16, at most 256.  A gathered row
+// then is a whole number of 32-byte MMA steps and at least two 16-byte chunks; rows shorter than a
+// 128-byte swizzle span (fp16 C = 16 / 32 / 48, tf32 C = 16) fill the front of a span and the rest of
+// the span is never read.  Whether a shape also fits shared memory is decided by g3_plan / w3_plan.
 inline bool umma_supported(int c_in, int c_out, int elem_bytes) {
-  return (c_in * elem_bytes) % 128 == 0 && (c_out * elem_bytes) % 128 == 0 && c_in <= 256 && c_out <= 256;
+  (void)elem_bytes;
+  return c_in % 16 == 0 && c_out % 16 == 0 && c_in >= 16 && c_out >= 16 && c_in <= 256 && c_out <= 256;
 }
 
 constexpr int G3_TILE_M = 128;
@@ -60,9 +66,13 @@ constexpr int G3_SHARED_BYTES = (sizeof(G3Shared) + 15) & ~15;
 struct G3Config {
   int n_stage;  // gather stages in the ring
   int n_wbuf;   // weight buffers: 2 when they fit, else 1 (a change of offset then drains the MMAs)
-  int w_bytes;  // k_dim * n_dim * elem
-  int n_tbuf;   // TMEM accumulators: 4 when 4 x n_dim columns fit in the 512, else 2
+  int w_bytes;  // one weight operand in its tcgen05 layout (whole 128-byte spans)
+  int n_tbuf;   // TMEM accumulators: 4 when 4 x n_acc columns fit in the 512, else 2
   int tbuf_shift;  // log2(n_tbuf)
+  int kch;      // 128-byte K chunks (= stages) per tile: ceil(k_dim * elem / 128)
+  int n_acc;    // TMEM columns per accumulator: n_dim rounded up to whole 128-byte blocks of the output row
+  int n_mma;    // N of the MMA: n_acc for the MN-major weight operand (forward), n_dim for the K-major one (dgrad)
+  int smem;     // dynamic shared memory of the launch
 };
 
 // one lane polls, the warp learns the outcome
@@ -124,7 +134,8 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_seg = p.k_vol + 1;
-  const int kch = p.k_dim / EPR;  // 128-byte K chunks per gathered row
+  const int kch = cfg.kch;                   // 128-byte K chunks per gathered row (the last one may be partly filled)
+  const int k_bytes = p.k_dim * ES;          // bytes of a gathered row: a multiple of 32
   const int n_stage = cfg.n_stage;
   volatile int* abort_flag = &sh->abort_flag;
 
@@ -144,7 +155,7 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
   }
   // TMEM allocation overlaps the first global loads below
   uint32_t tmem_cols = 32;
-  while (tmem_cols < (uint32_t)cfg.n_tbuf * p.n_dim) tmem_cols <<= 1;
+  while (tmem_cols < (uint32_t)(cfg.n_tbuf * cfg.n_acc)) tmem_cols <<= 1;
   if (warp == G3_MMA_WARP) {
     tmem_alloc(smem_u32(&sh->tmem_base), tmem_cols);
     tmem_relinquish();
@@ -152,8 +163,7 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
   // everything above touches no global memory; from here on the previous kernel's results may be needed
   griddep_wait();
   griddep_launch_dependents();
-  for (int s = tid; s <= p.k_vol; s += G3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
-  build_tile_table(G3_TILE_M, p.kpos, p.k_vol, p.dense_rows, tile_start);  // syncs the CTA
+  build_tile_table(G3_TILE_M, p.kpos, p.pairs, p.k_vol, p.dense_rows, kpos_s, tile_start);  // syncs the CTA
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -173,15 +183,20 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     // 16-31 their scatter entries (needed to skip pairs whose destination is outside the tensor).
     const int pw = warp - G3_PROD_WARP0;
     const int tp = tid - G3_PROD_WARP0 * 32;
-    const int pc = lane & 7, rsub = lane >> 3;  // this thread copies chunk pc of rows 16 pw + rsub + 4 j
+    // `lpr` lanes share a row, one 16-byte chunk each: 8 for rows of a whole span or more, 4 / 2 for 64- /
+    // 32-byte rows, so that short rows still keep every lane busy.  This thread copies chunk pc of the rows
+    // 16 pw + rsub + rpp j, j < n_pass.
+    const int lpr = k_bytes > 64 ? 8 : (k_bytes > 32 ? 4 : 2);
+    const int rpp = 32 / lpr, n_pass = 16 / rpp;  // rows per warp-wide copy: 4 / 8 / 16; copies per tile: 4 / 2 / 1
+    const int pc = lane % lpr, rsub = lane / lpr;
     const uint8_t* src = static_cast<const uint8_t*>(p.src);
     const uint8_t* wts = static_cast<const uint8_t*>(p.weights);
-    const size_t src_row_bytes = (size_t)p.k_dim * ES;
+    const size_t src_row_bytes = (size_t)k_bytes;
     const uint32_t w_row_bytes = (uint32_t)p.c_out * ES;
     uint32_t a_dst[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const uint32_t r = (uint32_t)(16 * pw + rsub + 4 * j);
+      const uint32_t r = (uint32_t)(16 * pw + rsub + rpp * j) & 127u;
       a_dst[j] = (r >> 3) * 1024u + (r & 7u) * 128u + (((uint32_t)pc ^ (r & 7u)) << 4);
     }
     const uint32_t ring = smem_u32(sRing) + (uint32_t)(pw * G3_RING_SLOTS * 128 + lane * 4);  // this lane's word of slot 0
@@ -194,8 +209,8 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     };
     // Weight matrix -> operand layout.  The matrix is `w_rows` rows of `cpr` 16-byte chunks; when cpr divides the
     // number of producer threads every thread keeps one chunk column and strides over rows (no division in the loop).
-    const int w_rows = TRANS_W ? p.n_dim : p.k_dim;
-    const int cpr = (TRANS_W ? p.k_dim : p.n_dim) * ES / 16;
+    const int w_rows = p.c_in;             // rows of W_k in global memory: n_dim of them for dgrad, k_dim for forward
+    const int cpr = p.c_out * ES / 16;     // 16-byte chunks per row
     const bool cpr_divides = (G3_PROD_THREADS % cpr) == 0;
     const uint32_t w_c = cpr_divides ? (uint32_t)(tp % cpr) : 0u;
     const int w_r0 = cpr_divides ? tp / cpr : 0, w_rstep = cpr_divides ? G3_PROD_THREADS / cpr : 0;
@@ -265,16 +280,19 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       bool valid[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        const int g = __shfl_sync(0xffffffffu, ev, rsub + 4 * j);
-        valid[j] = g >= 0;
+        const int g = __shfl_sync(0xffffffffu, ev, (rsub + rpp * j) & 15);
+        valid[j] = g >= 0 && j < n_pass;
         rsrc[j] = src + (size_t)max(g, 0) * src_row_bytes + (size_t)pc * 16;
       }
       for (int kc = 0; kc < kch && ok; ++kc) {
         ok = g3_wait(&sh->empty[s], ph ^ 1u, abort_flag);
         if (!ok) break;
         const uint32_t st = smem_u32(sStage + (size_t)s * G3_STAGE_BYTES);
+        if (kc * 128 + pc * 16 < k_bytes) {  // the last chunk of a row that is no whole number of spans is partly filled
 #pragma unroll
-        for (int j = 0; j < 4; ++j) cp_async16(st + a_dst[j], rsrc[j] + (size_t)kc * 128, valid[j]);
+          for (int j = 0; j < 4; ++j)
+            if (j < n_pass) cp_async16(st + a_dst[j], rsrc[j] + (size_t)kc * 128, valid[j]);
+        }
         // the stage's barrier hears from this thread when everything it has issued so far has landed
         cp_async_arrive_noinc(smem_u32(&sh->full[s]));
         if (++s == n_stage) { s = 0; ph ^= 1u; }
@@ -283,7 +301,7 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     }
   } else if (warp == G3_MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = make_idesc(TF32, false, !TRANS_W, G3_TILE_M, p.n_dim);
+    const uint32_t idesc = make_idesc(TF32, false, !TRANS_W, G3_TILE_M, cfg.n_mma);
     G3Walk cur;
     cur.init(tile_start, n_seg, t0);
     int s = 0;
@@ -303,7 +321,7 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       ok = g3_wait(&sh->tmem_empty[buf], (use & 1u) ^ 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + (uint32_t)buf * p.n_dim;
+      const uint32_t d_tmem = tmem_base + (uint32_t)(buf * cfg.n_acc);
       const uint32_t sw = smem_u32(sW + (size_t)wb * cfg.w_bytes);
       for (int kc = 0; kc < kch && ok; ++kc) {
         ok = g3_wait(&sh->full[s], ph, abort_flag);
@@ -312,8 +330,10 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
           fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
           tc_fence_after();
           const uint32_t sa = smem_u32(sStage + (size_t)s * G3_STAGE_BYTES);
+          const int n_ks = min(4, (k_bytes - kc * 128) >> 5);  // 32-byte MMA steps this chunk holds
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
+            if (ks >= n_ks) break;
             const uint64_t a_desc = make_sdesc(sa + ks * 32u, 16u, 1024u);
             uint64_t b_desc;
             if (!TRANS_W) {
@@ -347,7 +367,6 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     uint8_t* dst = static_cast<uint8_t*>(p.dst);
     uint8_t* patch = sPatch + warp * 4096;  // 32 rows x 128 bytes, private to the warp
     const uint32_t sw7 = (uint32_t)(lane & 7);
-    const uint32_t ch = (uint32_t)(lane & 7), rsub = (uint32_t)(lane >> 3);  // red: chunk ch of rows rsub + 4 u
     // map entries of tile row 32 q + lane (-1 beyond the tile)
     const uint32_t ring = smem_u32(sRing) + (uint32_t)((G3_PROD_WARPS + 2 * warp) * G3_RING_SLOTS * 128 + lane * 4);
     auto fetch_entries = [&](const G3Walk& w, int slot) {  // gather entry -> ring[slot], scatter entry -> ring[SLOTS + slot]
@@ -391,8 +410,12 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
         ok = g3_wait(&sh->tmem_full[buf], use & 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)buf * p.n_dim;
+        const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(buf * cfg.n_acc);
         for (uint32_t cb = 0; cb < row_bytes; cb += 128) {
+          // bytes of this block that belong to the row; `lpe` lanes share a row in the reds below
+          const uint32_t vb = min(128u, row_bytes - cb);
+          const uint32_t lpe = vb > 64 ? 8u : (vb > 32 ? 4u : 2u), rpe = 32u / lpe;
+          const uint32_t ch = (uint32_t)lane % lpe, rsub = (uint32_t)lane / lpe;  // red: chunk ch of rows rsub + rpe u
           const uint32_t col0 = cb / ES;
 #pragma unroll
           for (uint32_t c0 = 0; c0 < BLK_COLS; c0 += 32) {
@@ -427,12 +450,14 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
           }
           __syncwarp();
           uint8_t* dcol = dst + cb + (ch << 4);
+          const bool ch_ok = (ch << 4) < vb;
 #pragma unroll
           for (uint32_t u = 0; u < 8; ++u) {
-            const uint32_t r = rsub + 4 * u;
+            if (u >= lpe) break;  // 32 rows = lpe passes of rpe rows
+            const uint32_t r = rsub + rpe * u;
             const int sr = __shfl_sync(0xffffffffu, srow, r);
             const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
-            if (sr >= 0) {
+            if (sr >= 0 && ch_ok) {
               uint8_t* o = dcol + (size_t)sr * row_bytes;
               if (TF32) red_add_v4(reinterpret_cast<float*>(o), __uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
               else red_add_h8(reinterpret_cast<__half*>(o), v.x, v.y, v.z, v.w);
@@ -451,42 +476,59 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
   if (warp == G3_MMA_WARP) tmem_dealloc(tmem_base, tmem_cols);
 }
 
-// host launcher: 0 launched, 1 shape or pointers do not fit (caller takes the CUDA-core path), < 0 CUDA error
+// ---------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------
+// Shared-memory plan of a forward (trans = false) or dgrad (trans = true) launch.  Returns false when the
+// shape is outside what the kernel takes or does not fit `max_smem`: the one place that decides it, used by
+// the launcher and by the kernel-family query alike.
+inline bool g3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, bool trans, G3Config* cfg) {
+  if (!umma_supported(c_in, c_out, es)) return false;
+  const int k_dim = trans ? c_out : c_in, n_dim = trans ? c_in : c_out;
+  const int epr = 128 / es;
+  cfg->kch = (k_dim * es + 127) / 128;
+  cfg->n_acc = (n_dim + epr - 1) / epr * epr;
+  cfg->n_mma = trans ? n_dim : cfg->n_acc;
+  cfg->w_bytes = trans ? n_dim * 128 * cfg->kch : k_dim * 128 * (cfg->n_acc / epr);
+  cfg->n_tbuf = (4 * cfg->n_acc <= 512) ? 4 : 2;
+  cfg->tbuf_shift = cfg->n_tbuf == 4 ? 2 : 1;
+  const int table = ((2 * k_vol + 3) * 4 + 15) & ~15;
+  const int fixed = 1024 + G3_PATCH_BYTES + G3_RING_BYTES + G3_SHARED_BYTES + table;
+  // two weight buffers if at least four gather stages still fit beside them
+  cfg->n_wbuf = (fixed + 2 * cfg->w_bytes + 4 * G3_STAGE_BYTES <= max_smem) ? 2 : 1;
+  cfg->n_stage = (max_smem - fixed - cfg->n_wbuf * cfg->w_bytes) / G3_STAGE_BYTES;
+  if (cfg->n_stage > G3_MAX_STAGES) cfg->n_stage = G3_MAX_STAGES;
+  if (cfg->n_stage < 2) return false;
+  cfg->smem = fixed + cfg->n_wbuf * cfg->w_bytes + cfg->n_stage * G3_STAGE_BYTES;
+  return true;
+}
+
+// cudaFuncSetAttribute is needed once per kernel and device; `granted` remembers it (any thread may call)
 template <typename K>
-inline int g3_ensure_smem(K kernel, int bytes, int slot) {
-  static int granted[4][64] = {};  // [kernel][device]: cudaFuncSetAttribute is needed once per device
+inline int ensure_smem(K kernel, int bytes, std::atomic<int>* granted /* [64], by device */) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
-  if (granted[slot][dev] >= bytes) return 0;
+  if (granted[dev].load(std::memory_order_acquire) >= bytes) return 0;
   if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess) return -1;
-  granted[slot][dev] = bytes;
+  granted[dev].store(bytes, std::memory_order_release);
   return 0;
 }
 
+template <bool TF32, bool TRANS_W>
+inline int g3_launch(const GmsParams& p, const G3Config& cfg, cudaStream_t st, int sms, int max_smem) {
+  static std::atomic<int> granted[64];
+  if (int rc = ensure_smem(umma_gms3_kernel<TF32, TRANS_W>, max_smem, granted)) return rc;
+  return launch_pdl(umma_gms3_kernel<TF32, TRANS_W>, sms, G3_THREADS, (size_t)cfg.smem, st, p, cfg) == cudaSuccess ? 0 : -1;
+}
+
+// 0 launched, 1 the pointers are not 16-byte aligned or the shape has no plan (the caller takes the CUDA-core
+// path and counts it), < 0 CUDA error
 inline int launch_umma_gms3(const GmsParams& p, bool trans, bool f16, cudaStream_t st, int sms, int max_smem) {
-  const int es = f16 ? 2 : 4;
   if ((reinterpret_cast<uintptr_t>(p.src) | reinterpret_cast<uintptr_t>(p.weights) | reinterpret_cast<uintptr_t>(p.dst)) & 15) return 1;
   G3Config cfg;
-  cfg.w_bytes = p.k_dim * p.n_dim * es;
-  cfg.n_tbuf = (4 * p.n_dim <= 512) ? 4 : 2;
-  cfg.tbuf_shift = cfg.n_tbuf == 4 ? 2 : 1;
-  const int table = ((2 * p.k_vol + 3) * 4 + 15) & ~15;
-  const int fixed = 1024 + G3_PATCH_BYTES + G3_RING_BYTES + G3_SHARED_BYTES + table;
-  // two weight buffers if at least four gather stages still fit beside them
-  cfg.n_wbuf = (fixed + 2 * cfg.w_bytes + 4 * G3_STAGE_BYTES <= max_smem) ? 2 : 1;
-  cfg.n_stage = (max_smem - fixed - cfg.n_wbuf * cfg.w_bytes) / G3_STAGE_BYTES;
-  if (cfg.n_stage > G3_MAX_STAGES) cfg.n_stage = G3_MAX_STAGES;
-  if (cfg.n_stage < 2) return 1;
-  const int smem = fixed + cfg.n_wbuf * cfg.w_bytes + cfg.n_stage * G3_STAGE_BYTES;
-  int rc;
-  if (f16) {
-    if (trans) { rc = g3_ensure_smem(umma_gms3_kernel<false, true>, max_smem, 0); if (rc) return rc; if (launch_pdl(umma_gms3_kernel<false, true>, sms, G3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1; }
-    else       { rc = g3_ensure_smem(umma_gms3_kernel<false, false>, max_smem, 1); if (rc) return rc; if (launch_pdl(umma_gms3_kernel<false, false>, sms, G3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1; }
-  } else {
-    if (trans) { rc = g3_ensure_smem(umma_gms3_kernel<true, true>, max_smem, 2); if (rc) return rc; if (launch_pdl(umma_gms3_kernel<true, true>, sms, G3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1; }
-    else       { rc = g3_ensure_smem(umma_gms3_kernel<true, false>, max_smem, 3); if (rc) return rc; if (launch_pdl(umma_gms3_kernel<true, false>, sms, G3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1; }
-  }
-  return 0;
+  if (!g3_plan(p.c_in, p.c_out, f16 ? 2 : 4, p.k_vol, max_smem, trans, &cfg)) return 1;
+  if (f16) return trans ? g3_launch<false, true>(p, cfg, st, sms, max_smem) : g3_launch<false, false>(p, cfg, st, sms, max_smem);
+  return trans ? g3_launch<true, true>(p, cfg, st, sms, max_smem) : g3_launch<true, false>(p, cfg, st, sms, max_smem);
 }
 
 }  // namespace fgms

@@ -3,8 +3,11 @@
 //   dw[k] (c_in x c_out, fp32) += sum over the pairs j of offset k of feats[in_map[j]]^T (x) out_grad[out_map[j]]
 //
 // The pair index is the contraction index: both operands are gathered rows used MN-major.
-//   A = feats rows     [pb pairs x c_in ]   M = c_in  (tiles of 128 rows, or one tile of 64)
-//   B = out_grad rows  [pb pairs x c_out]   N = c_out
+//   A = feats rows     [pb pairs x c_in ]   M = c_in  (tiles of 128 rows; the last tile has 64 when at most 64 rows remain)
+//   B = out_grad rows  [pb pairs x c_out]   N = c_out rounded up to a whole 128-byte piece
+// Rows are staged in 128-byte pieces.  A piece that a short row fills only in part, or that exists only to
+// complete the last row tile, holds stale shared memory beyond the row: those values reach accumulator rows
+// >= c_in and columns >= c_out only, which are never written out.
 // One persistent CTA per SM walks a contiguous range of pb-pair stages.  The accumulator stays in TMEM
 // while consecutive stages belong to the same offset and is flushed with 16-byte vector reds to the
 // fp32 gradient when the offset changes (split-K across CTAs).
@@ -27,10 +30,7 @@ namespace fgms {
 constexpr int W3_EPI_WARPS = 4;
 constexpr int W3_MMA_WARP = 4;
 constexpr int W3_PROD_WARP0 = 5;
-#ifndef W3_PROD_WARPS_N
-#define W3_PROD_WARPS_N 8
-#endif
-constexpr int W3_PROD_WARPS = W3_PROD_WARPS_N;  // 8 or 16
+constexpr int W3_PROD_WARPS = 8;
 constexpr int W3_PROD_THREADS = W3_PROD_WARPS * 32;
 constexpr int W3_THREADS = (W3_PROD_WARP0 + W3_PROD_WARPS) * 32;
 __device__ __forceinline__ int w3_producer_index(int warp) { return warp - W3_PROD_WARP0; }  // < 0: no producer
@@ -51,9 +51,11 @@ constexpr int W3_SHARED_BYTES = (sizeof(W3Shared) + 15) & ~15;
 
 struct W3Config {
   int pb;         // pairs per stage: 32, 64 or 128
-  int n_mtile;    // 1 or 2 accumulator row tiles
-  int mtile_m;    // rows of each tile's MMA: 128 or 64
-  int alias;      // 1: the single tile has fewer real rows than mtile_m; extra rows repeat (LBO = 0)
+  int n_mtile;    // 1 or 2 accumulator row tiles: all of 128 rows but possibly the last
+  int last_m;     // rows of the last tile's MMA: 128, or 64 when at most 64 rows remain
+  int pa, pbp;    // 128-byte pieces per staged row of A (enough for every row tile) and of B (n_acc columns)
+  int n_acc;      // TMEM columns of one row tile: c_out rounded up to a whole piece
+  int smem;       // dynamic shared memory of the launch
   int n_buf;      // TMEM accumulator sets: 1, 2 or 4
   int buf_shift;  // log2(n_buf)
   int n_stage;    // a multiple of `group`
@@ -76,8 +78,8 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int pb = cfg.pb, n_stage = cfg.n_stage;
-  const uint32_t a_bytes = (uint32_t)pb * p.c_in * ES;
-  const uint32_t stage_bytes = (uint32_t)pb * (p.c_in + p.c_out) * ES;
+  const uint32_t a_bytes = (uint32_t)pb * 128u * cfg.pa;
+  const uint32_t stage_bytes = (uint32_t)pb * 128u * (cfg.pa + cfg.pbp);
   uint8_t* sStage = smem;
   uint8_t* sPatch = sStage + (size_t)n_stage * stage_bytes;
   W3Shared* sh = reinterpret_cast<W3Shared*>(sPatch + W3_PATCH_BYTES);
@@ -88,7 +90,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
   const int n_seg = p.k_vol + 1;
   volatile int* abort_flag = &sh->abort_flag;
   const uint32_t lbo = (uint32_t)pb * 128u;  // next 128 bytes of every gathered row
-  const uint32_t buf_cols = (uint32_t)cfg.n_mtile * p.c_out;
+  const uint32_t buf_cols = (uint32_t)(cfg.n_mtile * cfg.n_acc);
 
   if (tid == 0) {
     for (int s = 0; s < n_stage; ++s) {
@@ -112,8 +114,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
   // everything above touches no global memory; from here on the previous kernel's results may be needed
   griddep_wait();
   griddep_launch_dependents();
-  for (int s = tid; s <= p.k_vol; s += W3_THREADS) kpos_s[s] = __ldg(p.kpos + s);
-  build_tile_table(pb, p.kpos, p.k_vol, 0, tile_start);  // syncs the CTA
+  build_tile_table(pb, p.kpos, p.pairs, p.k_vol, 0, kpos_s, tile_start);  // syncs the CTA
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -132,8 +133,8 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     const int n_pass = rpw >> 2;         // a warp-wide copy covers 4 rows x 128 bytes
     const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
     const uint8_t* og = static_cast<const uint8_t*>(p.out_grad);
-    const int nha = p.c_in * ES / 128, nhb = p.c_out * ES / 128;  // 128-byte pieces per row: 1 .. 8
     const uint32_t a_row_bytes = (uint32_t)p.c_in * ES, b_row_bytes = (uint32_t)p.c_out * ES;
+    const int nha = (int)(a_row_bytes + 127) / 128, nhb = (int)(b_row_bytes + 127) / 128;  // 128-byte pieces per row: 1 .. 8
     // Lane (rs, c) = (lane / 8, lane % 8) copies 16-byte chunk c of every 128-byte piece of the rows
     // rs, rs + 4, ... of the warp's block: one shuffle and one address per row, then one cp.async per
     // piece at a fixed distance (128 bytes in global memory, `lbo` in shared memory).
@@ -196,12 +197,13 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
           const uint8_t* pa = feats_c + (size_t)max(ia, 0) * a_row_bytes;
           const uint8_t* pb_ = og_c + (size_t)max(ib, 0) * b_row_bytes;
           const uint32_t da = sa + dst_rel[u], db = sb + dst_rel[u];
+          // (the last piece of a row that is no whole number of pieces is filled in part)
 #pragma unroll
           for (int h = 0; h < 8; ++h)
-            if (h < nha) cp_async16_n(da + (uint32_t)h * lbo, pa + h * 128, na);
+            if (h < nha && (uint32_t)(h * 128 + cc * 16) < a_row_bytes) cp_async16_n(da + (uint32_t)h * lbo, pa + h * 128, na);
 #pragma unroll
           for (int h = 0; h < 8; ++h)
-            if (h < nhb) cp_async16_n(db + (uint32_t)h * lbo, pb_ + h * 128, nb);
+            if (h < nhb && (uint32_t)(h * 128 + cc * 16) < b_row_bytes) cp_async16_n(db + (uint32_t)h * lbo, pb_ + h * 128, nb);
         }
       }
       // the stage's barrier hears from this thread when everything it has issued so far has landed
@@ -211,10 +213,10 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     }
   } else if (warp == W3_MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
-    const uint32_t idesc = make_idesc(TF32, true, true, cfg.mtile_m, p.c_out);
+    const uint32_t idesc_full = make_idesc(TF32, true, true, 128, cfg.n_acc);
+    const uint32_t idesc_last = make_idesc(TF32, true, true, cfg.last_m, cfg.n_acc);
     const uint32_t sbo = TF32 ? 512u : 1024u, ltype = TF32 ? 1u : 2u;
-    const uint32_t a_lbo = cfg.alias ? 0u : lbo;
-    const uint32_t mtile_stride = (uint32_t)(cfg.mtile_m * ES / 128) * lbo;  // A start of the second row tile
+    const uint32_t mtile_stride = (uint32_t)ES * lbo;  // a 128-row tile spans 128 * ES / 128 pieces
     G3Walk cur;
     cur.init(tile_start, n_seg, t0);
     int s = 0, sg = 0, run_i = 0, cur_seg = -1;
@@ -246,9 +248,9 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
           const uint32_t kadv = (uint32_t)ks * UK * 128u;
           const uint64_t b_desc = make_sdesc(sb + kadv, lbo, sbo, ltype);
           for (int mt = 0; mt < cfg.n_mtile; ++mt) {
-            const uint64_t a_desc = make_sdesc(sa + kadv + mt * mtile_stride, a_lbo, sbo, ltype);
-            mma_ss<TF32>(tmem_base + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out, a_desc, b_desc, idesc,
-                         !(first && ks == 0));
+            const uint64_t a_desc = make_sdesc(sa + kadv + mt * mtile_stride, lbo, sbo, ltype);
+            mma_ss<TF32>(tmem_base + (uint32_t)buf * buf_cols + (uint32_t)(mt * cfg.n_acc), a_desc, b_desc,
+                         mt + 1 == cfg.n_mtile ? idesc_last : idesc_full, !(first && ks == 0));
           }
         }
         // one commit per group of stages (and one for the CTA's last stage, which nobody waits for)
@@ -286,7 +288,8 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
         // fp16 destination: 64 columns (128 bytes of fp16) of the warp's 32 rows per round
         __half* dwk16 = p.dw_f16 + (size_t)seg * p.c_in * p.c_out;
         for (int mt = 0; mt < cfg.n_mtile; ++mt) {
-          const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out;
+          const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * buf_cols + (uint32_t)(mt * cfg.n_acc);
+          const bool m128 = mt + 1 < cfg.n_mtile || cfg.last_m == 128;
           for (int c0 = 0; c0 < p.c_out; c0 += 64) {
 #pragma unroll
             for (int half_i = 0; half_i < 2; ++half_i) {
@@ -308,17 +311,18 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
             for (uint32_t u = 0; u < 8; ++u) {
               const uint32_t r = rsub + 4 * u;
               int m;
-              if (cfg.mtile_m == 128) m = mt * 128 + warp * 32 + (int)r;
-              else m = r < 16 ? warp * 16 + (int)r : -1;
+              if (m128) m = mt * 128 + warp * 32 + (int)r;
+              else m = r < 16 ? mt * 128 + warp * 16 + (int)r : -1;
               const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
-              if (m >= 0 && m < p.c_in) red_add_h8(dwk16 + (size_t)m * p.c_out + c0 + (ch << 3), v.x, v.y, v.z, v.w);
+              if (m >= 0 && m < p.c_in && c0 + (int)(ch << 3) < p.c_out) red_add_h8(dwk16 + (size_t)m * p.c_out + c0 + (ch << 3), v.x, v.y, v.z, v.w);
             }
             __syncwarp();
           }
         }
       } else
       for (int mt = 0; mt < cfg.n_mtile; ++mt) {
-        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * buf_cols + (uint32_t)mt * p.c_out;
+        const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)buf * buf_cols + (uint32_t)(mt * cfg.n_acc);
+        const bool m128 = mt + 1 < cfg.n_mtile || cfg.last_m == 128;
         for (int c0 = 0; c0 < p.c_out; c0 += 32) {
           uint32_t v0[16], v1[16];
           tmem_ld16(taddr + c0, v0);
@@ -335,10 +339,10 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
             const uint32_t r = rsub + 4 * u;  // TMEM lane (within the warp's quarter) whose row this is
             // M = 128: lane r of warp w is row 32 w + r; M = 64: row i lives in lane (i / 16) * 32 + i % 16
             int m;
-            if (cfg.mtile_m == 128) m = mt * 128 + warp * 32 + (int)r;
-            else m = r < 16 ? warp * 16 + (int)r : -1;
+            if (m128) m = mt * 128 + warp * 32 + (int)r;
+            else m = r < 16 ? mt * 128 + warp * 16 + (int)r : -1;
             const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
-            if (m >= 0 && m < p.c_in)
+            if (m >= 0 && m < p.c_in && c0 + (int)(ch << 2) < p.c_out)
               red_add_v4(dwk + (size_t)m * p.c_out + c0 + (ch << 2), __uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
           }
           __syncwarp();
@@ -358,23 +362,25 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
   if (warp == W3_MMA_WARP) tmem_dealloc(tmem_base, tmem_cols);
 }
 
-// Accumulator row tiling for c_in: whole 128-row tiles, a single 64-row tile, or a single tile whose
-// rows beyond c_in repeat the real ones.  Returns false for shapes that are not covered (e.g. 192 rows).
-inline bool w3_config(int c_in, int c_out, int es, int max_smem, int k_vol, int pb_cap, W3Config* cfg) {
-  const int span = 128 / es;  // rows per 128-byte span of a gathered feature row
-  if (c_in % 128 == 0) { cfg->n_mtile = c_in / 128; cfg->mtile_m = 128; cfg->alias = 0; }
-  else if (c_in == 64) { cfg->n_mtile = 1; cfg->mtile_m = 64; cfg->alias = 0; }
-  else if (c_in == span) { cfg->n_mtile = 1; cfg->mtile_m = 64; cfg->alias = 1; }  // tf32, 32 rows
-  else return false;
-  if (cfg->n_mtile > 2) return false;
-  const int buf_cols = cfg->n_mtile * c_out;
+// Plan of a launch: accumulator row tiling for c_in, pieces per staged row, stage size and count.  Returns
+// false for shapes the kernel does not take or that do not fit `max_smem`; used by the launcher and by the
+// kernel-family query alike.
+inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Config* cfg) {
+  if (!umma_supported(c_in, c_out, es)) return false;
+  const int epr = 128 / es;  // elements per 128-byte piece
+  cfg->n_mtile = (c_in + 127) / 128;
+  cfg->last_m = (c_in - 128 * (cfg->n_mtile - 1)) <= 64 ? 64 : 128;
+  cfg->pa = (cfg->n_mtile - 1) * es + (cfg->last_m == 128 ? es : es / 2);  // a 128-row tile reads 128 / epr = es pieces
+  cfg->n_acc = (c_out + epr - 1) / epr * epr;
+  cfg->pbp = cfg->n_acc / epr;
+  const int buf_cols = cfg->n_mtile * cfg->n_acc;
   if (buf_cols > 512) return false;
   cfg->n_buf = 4 * buf_cols <= 512 ? 4 : (2 * buf_cols <= 512 ? 2 : 1);
   cfg->buf_shift = cfg->n_buf == 4 ? 2 : (cfg->n_buf == 2 ? 1 : 0);
   // pairs per stage: 4, 8 or 16 rows per producer warp
-  int pb = pb_cap;
+  int pb = W3_MAX_PB;
   const int fixed = 1024 + W3_PATCH_BYTES + W3_SHARED_BYTES + (((2 * k_vol + 3) * 4 + 15) & ~15);
-  const int row_bytes = (c_in + c_out) * es;
+  const int row_bytes = 128 * (cfg->pa + cfg->pbp);
   while (pb > 32 && (max_smem - fixed) / (pb * row_bytes) < 3) pb >>= 1;  // keep at least three stages in flight
   int n_stage = (max_smem - fixed) / (pb * row_bytes);
   if (n_stage > W3_MAX_STAGES) n_stage = W3_MAX_STAGES;
@@ -385,35 +391,24 @@ inline bool w3_config(int c_in, int c_out, int es, int max_smem, int k_vol, int 
     if ((n_stage - n_stage % g) / g >= 3) { cfg->group = g; n_stage -= n_stage % g; break; }
   cfg->pb = pb;
   cfg->n_stage = n_stage;
+  cfg->smem = fixed + n_stage * pb * row_bytes;
   return true;
 }
 
-// host launcher: 0 launched, 1 shape or pointers do not fit (caller takes the CUDA-core path), < 0 CUDA error
+template <bool TF32>
+inline int w3_launch(const WgradParams& p, const W3Config& cfg, cudaStream_t st, int sms, int max_smem) {
+  static std::atomic<int> granted[64];
+  if (int rc = ensure_smem(umma_wgrad3_kernel<TF32>, max_smem, granted)) return rc;
+  return launch_pdl(umma_wgrad3_kernel<TF32>, sms, W3_THREADS, (size_t)cfg.smem, st, p, cfg) == cudaSuccess ? 0 : -1;
+}
+
+// 0 launched, 1 the pointers are not 16-byte aligned or the shape has no plan (the caller takes the CUDA-core
+// path and counts it), < 0 CUDA error
 inline int launch_umma_wgrad3(const WgradParams& p, bool f16, cudaStream_t st, int sms, int max_smem) {
-  const int es = f16 ? 2 : 4;
   if ((reinterpret_cast<uintptr_t>(p.feats) | reinterpret_cast<uintptr_t>(p.out_grad) | reinterpret_cast<uintptr_t>(p.dw) | reinterpret_cast<uintptr_t>(p.dw_f16)) & 15) return 1;
   W3Config cfg;
-  static const int pb_cap = [] { const char* e = getenv("FGMS_B200_WGRAD_PB"); const int v = e ? atoi(e) : W3_MAX_PB; return (v == 32 || v == 64 || v == 128) ? v : W3_MAX_PB; }();
-  if (!w3_config(p.c_in, p.c_out, es, max_smem, p.k_vol, pb_cap, &cfg)) return 1;
-  const int smem = 1024 + W3_PATCH_BYTES + W3_SHARED_BYTES + (((2 * p.k_vol + 3) * 4 + 15) & ~15) +
-                   cfg.n_stage * cfg.pb * (p.c_in + p.c_out) * es;
-  static int granted[2][64] = {};  // cudaFuncSetAttribute is needed once per device and kernel
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return -1;
-  if (f16) {
-    if (granted[0][dev] < max_smem) {
-      if (cudaFuncSetAttribute(umma_wgrad3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) return -1;
-      granted[0][dev] = max_smem;
-    }
-    if (launch_pdl(umma_wgrad3_kernel<false>, sms, W3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1;
-  } else {
-    if (granted[1][dev] < max_smem) {
-      if (cudaFuncSetAttribute(umma_wgrad3_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, max_smem) != cudaSuccess) return -1;
-      granted[1][dev] = max_smem;
-    }
-    if (launch_pdl(umma_wgrad3_kernel<true>, sms, W3_THREADS, (size_t)smem, st, p, cfg) != cudaSuccess) return -1;
-  }
-  return 0;
+  if (!w3_plan(p.c_in, p.c_out, f16 ? 2 : 4, p.k_vol, max_smem, &cfg)) return 1;
+  return f16 ? w3_launch<false>(p, cfg, st, sms, max_smem) : w3_launch<true>(p, cfg, st, sms, max_smem);
 }
 
 }  // namespace fgms

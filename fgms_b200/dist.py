@@ -21,7 +21,8 @@ import numpy as np
 
 from .maps import KernelMap
 
-__all__ = ["balanced_row_ranges", "shard_pairs_by_rows", "allreduce_sum_", "SceneParallelLayer"]
+__all__ = ["balanced_row_ranges", "shard_pairs_by_rows", "shard_map_device", "MapShard", "allreduce_sum_",
+           "SceneParallelLayer", "BoundSceneLayer"]
 
 
 def balanced_row_ranges(rows: np.ndarray, n_rows: int, world: int) -> np.ndarray:
@@ -60,6 +61,46 @@ def shard_pairs_by_rows(km: KernelMap, world: int, by: str = "out"):
                                 np.ascontiguousarray(km.imap[sel]), np.ascontiguousarray(km.omap[sel]),
                                 km.out_coords))
     return shards, bounds
+
+
+class MapShard:
+    """One rank's cut of a kernel map, as tensors on the device of the map it was cut from."""
+
+    def __init__(self, kpos, imap, omap, row_range):
+        self.kpos, self.imap, self.omap, self.row_range = kpos, imap, omap, row_range
+
+    @property
+    def pairs(self) -> int:
+        return int(self.imap.numel())
+
+
+def shard_map_device(kpos, imap, omap, n_rows: int, rank: int, world: int, by: str = "out") -> MapShard:
+    """``shard_pairs_by_rows`` for one rank, computed where the map lives (tensor operations on the map's own
+    device; nothing is copied to the host but the two range boundaries).
+
+    The row ranges are the same balanced ones: boundaries on the cumulative pair histogram of the key map
+    (``out_map`` for ``by="out"``, ``in_map`` for ``by="in"``).  The rank keeps the pairs whose key row falls
+    in its range, in their original order, and ``kpos`` is re-derived from the per-offset counts of the kept
+    pairs.  Every rank computes the same boundaries from the same map, so no communication is needed."""
+    import torch
+    key = omap if by == "out" else imap
+    k_vol = kpos.numel() - 1
+    pairs = key.numel()
+    key64 = key.long()
+    hist = torch.bincount(key64, minlength=n_rows) if pairs else torch.zeros(n_rows, dtype=torch.long, device=key.device)
+    cum = torch.cat([hist.new_zeros(1), torch.cumsum(hist, 0)])
+    total = int(pairs)
+    # first row index whose cumulative count reaches total * r / world  (numpy: searchsorted(cum, x, side="left"))
+    targets = torch.tensor([total * r / world for r in (rank, rank + 1)], dtype=torch.float64, device=key.device)
+    b = torch.searchsorted(cum.double(), targets, right=False).clamp(max=n_rows).tolist()
+    lo = 0 if rank == 0 else int(b[0])
+    hi = n_rows if rank == world - 1 else int(b[1])
+    hi = max(hi, lo)
+    keep = (key64 >= lo) & (key64 < hi)
+    seg = torch.searchsorted(kpos[1:].long().contiguous(), torch.arange(pairs, device=key.device), right=True)
+    knnz = torch.bincount(seg[keep], minlength=k_vol)[:k_vol]
+    new_kpos = torch.cat([knnz.new_zeros(1), torch.cumsum(knnz, 0)]).to(torch.int32)
+    return MapShard(new_kpos.contiguous(), imap[keep].contiguous(), omap[keep].contiguous(), (lo, hi))
 
 
 def world_size(group=None) -> int:
@@ -134,7 +175,8 @@ class BoundSceneLayer:
     (the tensors must stay alive and keep their storage while the object is used).
     """
 
-    def __init__(self, feats, weights, grad_out, out, in_grad, w_grad, kpos, imap, omap, arch80: bool, group=None):
+    def __init__(self, feats, weights, grad_out, out, in_grad, w_grad, kpos, imap, omap, arch80: bool, group=None,
+                 exchange: bool = True):
         import torch
         from . import _lib, backend
         k_vol = backend._common(feats, weights, kpos, imap, omap)
@@ -151,14 +193,18 @@ class BoundSceneLayer:
         self.fp16 = feats.dtype == torch.float16
         dtype, math = backend._dtype_math(feats, arch80)
         self.multi = world_size(group) > 1
+        # exchange = False keeps the multi-rank form of the step (fp32 sums, final addition) but skips the
+        # all-reduce: the step's kernels alone, which is how the collective's exposed time is measured
+        self.exchange = exchange and self.multi
         n_in, n_out, c_in, c_out = feats.size(0), out.size(0), weights.size(1), weights.size(2)
         p = lambda t: t.data_ptr() if t.numel() > 0 else None
-        self._fwd_args = (p(feats), p(weights), p(out), p(kpos), None, p(imap), p(omap), n_in, n_out, c_in, c_in, c_out,
-                          k_vol, 0, dtype, math, 0)
-        self._dgrad_args = (p(grad_out), p(weights), p(in_grad), p(kpos), p(imap), p(omap), n_in, n_out, c_in, c_out, k_vol,
-                            dtype, math)
+        pairs = imap.numel()
+        self._fwd_args = (p(feats), p(weights), p(out), p(kpos), None, p(imap), p(omap), pairs, n_in, n_out, c_in, c_in,
+                          c_out, k_vol, 0, dtype, math, 0)
+        self._dgrad_args = (p(grad_out), p(weights), p(in_grad), p(kpos), p(imap), p(omap), pairs, n_in, n_out, c_in, c_out,
+                            k_vol, dtype, math)
         self.w_grad, self.part, ws_ptr, ws_bytes, accumulate = w_grad, None, None, 0, 1
-        if self.fp16 and (self.multi or backend.kernel_family("wgrad", c_in, c_out, feats.dtype, arch80) != "tcgen05"):
+        if self.fp16 and (self.multi or backend.kernel_family("wgrad", c_in, c_out, feats.dtype, arch80, k_vol) != "tcgen05"):
             ws = backend.wgrad_workspace(c_in, c_out, k_vol, feats.device)
             ws_ptr, ws_bytes = ws.data_ptr(), ws.numel() * 4
             if self.multi:
@@ -166,28 +212,33 @@ class BoundSceneLayer:
         elif not self.fp16 and self.multi:
             self.part = torch.zeros_like(w_grad)                   # fp32 storage: sums of this rank, all-reduced, then added
         target = self.part if (self.part is not None and not self.fp16) else w_grad
-        self._wgrad_args = (p(feats), p(grad_out), p(target), p(kpos), p(imap), p(omap), n_in, n_out, c_in, c_out, k_vol,
-                            dtype, math, ws_ptr, ws_bytes, accumulate)
+        self._wgrad_args = (p(feats), p(grad_out), p(target), p(kpos), p(imap), p(omap), pairs, n_in, n_out, c_in, c_out,
+                            k_vol, dtype, math, ws_ptr, ws_bytes, accumulate)
 
     def _stream(self):
         import torch
         return torch.cuda.current_stream(self.device).cuda_stream
 
     def forward(self):
-        self._check(self._L.fgms_b200_fusion_fwd(*self._fwd_args, self._stream()))
+        import torch
+        with torch.cuda.device(self.device):  # the library launches on the current device
+            self._check(self._L.fgms_b200_fusion_fwd(*self._fwd_args, self._stream()))
 
     def backward(self):
         """wgrad first, its all-reduce beside dgrad, then the sums are added to ``w_grad``."""
+        import torch
         import torch.distributed as dist
-        st = self._stream()
-        if self.part is not None and not self.fp16:
-            self.part.zero_()
-        self._check(self._L.fgms_b200_wgrad(*self._wgrad_args, st))
-        work = dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group, async_op=True) if self.multi else None
-        self._check(self._L.fgms_b200_dgrad(*self._dgrad_args, st))
-        if work is not None:
-            work.wait()
-            if self.fp16:
-                self._check(self._L.fgms_b200_wgrad_finalize(self.w_grad.data_ptr(), self.part.data_ptr(), self.w_grad.numel(), st))
-            else:
-                self.w_grad += self.part
+        with torch.cuda.device(self.device):  # the library launches on the current device
+            st = self._stream()
+            if self.part is not None and not self.fp16:
+                self.part.zero_()
+            self._check(self._L.fgms_b200_wgrad(*self._wgrad_args, st))
+            work = dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group, async_op=True) if self.exchange else None
+            self._check(self._L.fgms_b200_dgrad(*self._dgrad_args, st))
+            if work is not None:
+                work.wait()
+            if self.multi:
+                if self.fp16:
+                    self._check(self._L.fgms_b200_wgrad_finalize(self.w_grad.data_ptr(), self.part.data_ptr(), self.w_grad.numel(), st))
+                else:
+                    self.w_grad += self.part

@@ -16,7 +16,7 @@ import torch
 
 from . import backend
 
-__all__ = ["sparse_conv", "SparseConv3d"]
+__all__ = ["sparse_conv", "SparseConv3d", "SparseUNet"]
 
 
 class _SparseConvFunction(torch.autograd.Function):
@@ -62,3 +62,29 @@ class SparseConv3d(torch.nn.Module):
 
     def forward(self, feats: torch.Tensor, kmap) -> torch.Tensor:
         return sparse_conv(feats, self.weight, kmap, self.arch80)
+
+
+class SparseUNet(torch.nn.Module):
+    """The encoder-decoder stack of :mod:`fgms_b200.unet` as an ``nn.Module`` over the autograd operator: one
+    :class:`SparseConv3d` per layer of the specification, decoder skips added to the transposed convolutions'
+    outputs.  ``forward(feats, umaps)`` takes the kernel maps of all resolutions (``unet.build_unet_maps``)."""
+
+    def __init__(self, spec, dtype=torch.float16, device="cuda", arch80: bool = True):
+        super().__init__()
+        self.spec = list(spec)
+        self.layers = torch.nn.ModuleList(
+            SparseConv3d(l.c_in, l.c_out, l.k_vol, dtype=dtype, device=device, arch80=arch80) for l in self.spec)
+
+    def load_weights(self, weights):
+        with torch.no_grad():
+            for layer, w in zip(self.layers, weights):
+                layer.weight.copy_(torch.as_tensor(w).to(layer.weight.device, layer.weight.dtype))
+
+    def forward(self, feats: torch.Tensor, umaps) -> torch.Tensor:
+        val = {"input": feats}
+        for spec, layer in zip(self.spec, self.layers):
+            y = layer(val[spec.src], umaps.of(spec))
+            if spec.skip is not None:
+                y = y + val[spec.skip]
+            val[spec.dst] = y
+        return val[self.spec[-1].dst]

@@ -12,6 +12,9 @@ recorded with every result.
 ``cfg4``          two overlaid 64-beam LiDAR sweeps voxelised at 5 cm (~145 k voxels),
                   3x3x3 submanifold, fp16 128→128
 ================  =====================================================================
+
+``cfg5`` is not one layer but a stack (``unet_workload``): the MinkUNet-style encoder-decoder of
+:mod:`fgms_b200.unet` over a batch of ~120 k-voxel surface scenes, fp16.
 """
 from __future__ import annotations
 
@@ -20,7 +23,8 @@ from functools import lru_cache
 
 from . import clouds, maps
 
-__all__ = ["Workload", "LayerTensors", "get", "NAMES", "flops", "algorithmic_bytes"]
+__all__ = ["Workload", "LayerTensors", "get", "NAMES", "flops", "algorithmic_bytes", "UNetWorkload", "unet_workload",
+           "layer_bytes"]
 
 NAMES = ("cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4")
 
@@ -102,3 +106,51 @@ class LayerTensors:
         self.qkpos = torch.from_numpy(self.qkpos_np).to(dev)
         self.dtype = torch.float16 if mode == "fp16" else torch.float32
         self.arch80 = mode != "fp32"  # the reference's flag: tensor cores for fp32 storage
+
+
+# ---------------------------------------------------------------------------------------------
+# cfg5: the encoder-decoder stack
+# ---------------------------------------------------------------------------------------------
+SCENE_PITCH = 4096  # scenes of a batch are placed this far apart along x: no kernel offset or parent voxel is shared
+
+
+@dataclass(frozen=True)
+class UNetWorkload:
+    """Inputs of one step of the stack: batched voxel coordinates, input features ``[n, c_in]`` and the gradient
+    of the output ``[n, widths[0]]`` (both fp16, seeded).  Weights come from ``unet.unet_weights`` once the maps exist."""
+
+    name: str
+    description: str
+    coords: object     # int32 [n, 3], unique, sorted lexicographically
+    feats: object      # float16 [n, c_in]
+    grad_out: object   # float16 [n, widths[0]]
+    scenes: int
+    seed: int
+    c_in: int = 4
+    widths: tuple = (32, 32, 64, 128, 256)
+
+
+@lru_cache(maxsize=None)
+def unet_workload(scenes: int = 1, first_scene: int = 0, voxels: int = 120_000, grid: int = 256, seed: int = 105) -> UNetWorkload:
+    """``scenes`` surface scenes of about ``voxels`` voxels each (the cfg2 generator, one seed per scene) batched
+    into one cloud; ``first_scene`` selects which scenes of the global batch (one per rank in multi-GPU runs)."""
+    import numpy as np
+    parts = []
+    for s in range(first_scene, first_scene + scenes):
+        c = clouds.surface_cloud(voxels, grid, seed + 17 * s).copy()
+        c[:, 0] += SCENE_PITCH * (s - first_scene)
+        parts.append(c)
+    coords = maps.unique_coords(np.concatenate(parts))
+    rng = np.random.default_rng(seed + 1000 * first_scene + scenes)
+    n = coords.shape[0]
+    feats = rng.standard_normal((n, 4), dtype=np.float32).astype(np.float16)
+    grad_out = (0.25 * rng.standard_normal((n, 32), dtype=np.float32)).astype(np.float16)
+    return UNetWorkload("cfg5", f"MinkUNet-style stack (stem 4->32, stages 32/64/128/256, mirrored decoder, 25 layers), "
+                        f"{scenes} surface scene(s) of ~{voxels // 1000}k voxels in {grid}^3, fp16",
+                        coords, feats, grad_out, scenes, seed)
+
+
+def layer_bytes(pairs: int, c_in: int, c_out: int, k_vol: int, elem: int, which: str) -> float:
+    """Algorithmic bytes of one pass of a layer (same model as ``algorithmic_bytes``)."""
+    w = k_vol * c_in * c_out
+    return pairs * (c_in + c_out) * elem + 8 * pairs + w * (4 if which == "wgrad" else elem)

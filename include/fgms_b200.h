@@ -12,7 +12,12 @@
  *   kernel     [k_vol, c_in, c_out]       one weight matrix per kernel offset
  *   out_feats  [n_out, c_out]             accumulated into (caller zeroes it)
  *   kpos       int32 [k_vol + 1]          start of each offset's slice of the maps
- *   in_map / out_map  int32 [kpos[k_vol]] flat, offset-major (input row, output row) pairs
+ *   in_map / out_map  int32 [map_len]     flat, offset-major (input row, output row) pairs
+ *   map_len                               entries each of the two maps holds (>= kpos[k_vol])
+ *
+ * Nothing read from device memory is trusted with an address: every kpos entry is clamped to
+ * [0, map_len] before it positions a map read, and a map entry outside [0, n_in) / [0, n_out) makes
+ * its pair a no-op.  Both are counted (fgms_b200_device_status); results are then incomplete.
  *
  * Every function returns FGMS_OK (0) or a negative FGMS_ERR_* code and never throws; the
  * text of the last error of the calling thread is available from fgms_b200_last_error().
@@ -64,8 +69,8 @@ extern "C" {
  * reference (beta = 0, backend/spconv.cu:55-56,76-106), out_feats is OVERWRITTEN, not accumulated. */
 int fgms_b200_fusion_fwd(const void* in_feats, const void* kernel, void* out_feats,
                          const int32_t* kpos, const int32_t* qkpos, const int32_t* in_map,
-                         const int32_t* out_map, int n_in, int n_out, int c_in, int kernel_c_in,
-                         int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                         const int32_t* out_map, int64_t map_len, int n_in, int n_out, int c_in,
+                         int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                          int separate_mid, void* stream);
 
 /* Per-offset ("sequential") forward.  Replaces ConvolutionForward (backend/spconv.cu:249-411;
@@ -75,15 +80,15 @@ int fgms_b200_fusion_fwd(const void* in_feats, const void* kernel, void* out_fea
  * (beta = 1, backend/spconv.cu:282-283,378-410) without overwriting. */
 int fgms_b200_seq_fwd(const void* in_feats, const void* kernel, void* out_feats,
                       const int32_t* kernel_nnz_host, const int32_t* kpos, const int32_t* in_map,
-                      const int32_t* out_map, int n_in, int n_out, int c_in, int kernel_c_in,
-                      int c_out, int k_vol, int64_t sum_nnz, int dtype, int math, int separate_mid,
-                      void* stream);
+                      const int32_t* out_map, int64_t map_len, int n_in, int n_out, int c_in,
+                      int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                      int separate_mid, void* stream);
 
 /* Input gradient:  in_grad[in_map[j]] += out_grad[out_map[j]] . kernel[k(j)]^T.
  * First launch of ConvolutionBackward (backend/spconv.cu:454-461 fp16, 553-560 tf32). */
 int fgms_b200_dgrad(const void* out_grad, const void* kernel, void* in_grad, const int32_t* kpos,
-                    const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
-                    int c_out, int k_vol, int dtype, int math, void* stream);
+                    const int32_t* in_map, const int32_t* out_map, int64_t map_len, int n_in, int n_out,
+                    int c_in, int c_out, int k_vol, int dtype, int math, void* stream);
 
 /* Weight gradient:  kernel_grad[k] += sum over the pairs of offset k of in[in_map[j]]^T (x) out_grad[out_map[j]].
  * Second launch of ConvolutionBackward (backend/spconv.cu:495-548 fp16, 562-569 tf32).
@@ -95,15 +100,15 @@ int fgms_b200_dgrad(const void* out_grad, const void* kernel, void* in_grad, con
  * accumulate_into_kernel_grad == 0 leaves kernel_grad untouched (fp16 only): the caller reduces
  * the workspace across ranks and calls fgms_b200_wgrad_finalize itself.
  * fp16 storage with workspace == NULL and accumulate_into_kernel_grad != 0 selects the single-launch
- * form for channel counts the tensor-core kernel covers (fgms_b200_kernel_family(2, ...) == 1): every
+ * form for shapes the tensor-core kernel covers (fgms_b200_kernel_family(2, ...) == 1): every
  * CTA sums its share of an offset's pairs in fp32 and adds that partial sum, rounded to fp16, straight
  * into kernel_grad with fp16 atomics — no clearing, no second kernel, a few fp16 roundings per value
  * (the reference accumulates every product in fp16, backend/spconv.cu:495-548).  Other channel counts
  * return FGMS_ERR_WORKSPACE without a workspace. */
 int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_grad,
-                    const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in,
-                    int n_out, int c_in, int c_out, int k_vol, int dtype, int math, void* workspace,
-                    size_t workspace_bytes, int accumulate_into_kernel_grad, void* stream);
+                    const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int64_t map_len,
+                    int n_in, int n_out, int c_in, int c_out, int k_vol, int dtype, int math,
+                    void* workspace, size_t workspace_bytes, int accumulate_into_kernel_grad, void* stream);
 
 /* kernel_grad (fp16) += workspace (fp32), element-wise over k_vol * c_in * c_out values. */
 int fgms_b200_wgrad_finalize(void* kernel_grad_f16, const void* workspace_f32, int64_t count,
@@ -130,15 +135,15 @@ size_t fgms_b200_wgrad_workspace_bytes(int c_in, int c_out, int k_vol, int dtype
 #define FGMS_NOALLOC_MAX_ELEMS (512 * 1024)
 int fgms_b200_wgrad_f16_noalloc(const void* in_feats, const void* out_grad, void* kernel_grad,
                                 const int32_t* kpos, const int32_t* in_map, const int32_t* out_map,
-                                int n_in, int n_out, int c_in, int c_out, int k_vol, int math,
-                                void* stream);
+                                int64_t map_len, int n_in, int n_out, int c_in, int c_out, int k_vol,
+                                int math, void* stream);
 
 /* Both gradients.  Replaces ConvolutionBackward (backend/spconv.cu:414-571; Python name
  * fgms_bwd_cuda).  separate_mid is accepted and ignored, as in the reference. */
 int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel, void* in_grad,
                   void* kernel_grad, const int32_t* kpos, const int32_t* qkpos,
-                  const int32_t* in_map, const int32_t* out_map, int n_in, int n_out, int c_in,
-                  int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
+                  const int32_t* in_map, const int32_t* out_map, int64_t map_len, int n_in, int n_out,
+                  int c_in, int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                   int separate_mid, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
@@ -181,8 +186,16 @@ int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const in
                             int32_t* out_map_t, void* workspace, size_t workspace_bytes, void* stream);
 
 /* Which kernel family the dispatch picks for a shape: 0 = CUDA-core (SIMT), 1 = tcgen05.
- * pass: 0 forward, 1 dgrad, 2 wgrad. */
-int fgms_b200_kernel_family(int pass, int c_in, int c_out, int dtype, int math);
+ * pass: 0 forward, 1 dgrad, 2 wgrad.  The answer comes from the same plan the launch uses (channel
+ * counts multiples of 16 and at most 256, and the operands of this k_vol fitting the current device's
+ * shared memory), so it is what a call with 16-byte aligned tensors will run.  The reference makes the
+ * same choice inside its dispatch and does not expose it (backend/spconv.cu:108-245). */
+int fgms_b200_kernel_family(int pass, int c_in, int c_out, int k_vol, int dtype, int math);
+
+/* Number of launches of this process that the plan above put on tcgen05 but that ran on the CUDA-core
+ * kernels instead because a tensor's base address was not 16-byte aligned.  Such a call is correct but
+ * many times slower; a caller that cares asserts that this stays 0. */
+int64_t fgms_b200_fallback_count(void);
 
 /* Device-side problem counter of the current device: number of map entries outside
  * [0, n_in) / [0, n_out) that kernels skipped plus bounded waits that ran out, since the last

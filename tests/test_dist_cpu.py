@@ -105,3 +105,20 @@ def test_weight_gradient_allreduce_two_ranks():
 def test_allreduce_is_a_noop_without_a_process_group():
     t = torch.ones(4)
     assert allreduce_sum_(t) is t and t.sum() == 4
+
+
+@pytest.mark.parametrize("world", [1, 2, 5, 8])
+@pytest.mark.parametrize("by", ["out", "in"])
+def test_tensor_side_cut_equals_the_numpy_cut(world, by):
+    """``shard_map_device`` (tensor operations on the map's device; CPU tensors here) gives every rank exactly the
+    shard ``shard_pairs_by_rows`` gives it."""
+    from fgms_b200.dist import shard_map_device
+    km, *_ = _problem()
+    shards, bounds = shard_pairs_by_rows(km, world, by)
+    t = lambda a: torch.from_numpy(a)
+    n_rows = km.n_out if by == "out" else km.n_in
+    for r, s in enumerate(shards):
+        cut = shard_map_device(t(km.kpos), t(km.imap), t(km.omap), n_rows, r, world, by)
+        assert cut.row_range == (int(bounds[r]), int(bounds[r + 1]))
+        assert np.array_equal(cut.kpos.numpy(), s.kpos)
+        assert np.array_equal(cut.imap.numpy(), s.imap) and np.array_equal(cut.omap.numpy(), s.omap)

@@ -18,13 +18,30 @@ def _sub_map(n, grid, seed):
     return maps.build_submanifold_map(clouds.uniform_cloud(n, grid, seed))
 
 
+def expected_family(mode, c_in, c_out, pass_="fwd"):
+    """The dispatch rule, restated: tensor cores for tf32 / fp16 arithmetic when both channel counts are
+    multiples of 16 and at most 256 (and the operands fit shared memory, which only tf32 256 x 256 forward and
+    dgrad do not)."""
+    if mode == "fp32" or c_in % 16 or c_out % 16 or max(c_in, c_out) > 256:
+        return "simt"
+    if mode == "tf32" and c_in == 256 and c_out == 256 and pass_ != "wgrad":
+        return "simt"
+    return "tcgen05"
+
+
 def _check_all(p: Problem, tol=None):
     from fgms_b200 import backend
     tol = TOL[p.mode] if tol is None else tol
+    # a parity case must not pass on a slower kernel family than the shape is meant to run on
+    for pass_ in ("fwd", "dgrad", "wgrad"):
+        assert backend.kernel_family(pass_, p.c_in, p.c_out, p.dtype, p.arch80, p.km.k_vol) == \
+            expected_family(p.mode, p.c_in, p.c_out, pass_), (pass_, p.mode, p.c_in, p.c_out)
+    fallbacks = backend.fallback_count()
     backend.device_status(reset=True)
     out = p.run_fwd()
     in_grad, w_grad = p.run_bwd()
     assert backend.device_status() == 0
+    assert backend.fallback_count() == fallbacks, "a launch fell back to the CUDA-core kernels"
     e = (err(out, p.ref_fwd()), err(in_grad, p.ref_dgrad()), err(w_grad, p.ref_wgrad()))
     assert max(e) <= tol, f"fwd/dgrad/wgrad errors {e} exceed {tol} ({p.mode}, {p.c_in}->{p.c_out})"
     return e
@@ -52,8 +69,9 @@ def test_golden_fixtures_fp32(golden):
 
 
 @pytest.mark.parametrize("mode", MODES)
-@pytest.mark.parametrize("c_in,c_out", [(1, 1), (3, 5), (4, 32), (16, 16), (17, 33), (32, 64), (64, 32), (64, 64),
-                                        (48, 80), (128, 128), (96, 128), (128, 64), (256, 128), (128, 256), (192, 64)])
+@pytest.mark.parametrize("c_in,c_out", [(1, 1), (3, 5), (4, 32), (16, 16), (17, 33), (32, 32), (32, 64), (64, 32), (64, 64),
+                                        (48, 80), (128, 128), (96, 128), (128, 64), (256, 128), (128, 256), (192, 64),
+                                        (160, 96), (224, 32), (16, 256), (256, 256)])
 def test_channel_classes_submanifold(mode, c_in, c_out):
     p = Problem(_sub_map(1500, 14, c_in * 131 + c_out), c_in, c_out, seed=c_in + 7 * c_out, mode=mode)
     _check_all(p)
@@ -168,7 +186,7 @@ def test_fp16_wgrad_both_forms(c_in, c_out):
     agree with the oracle, accumulate into kernel_grad, and the workspace form leaves the fp32 sums behind."""
     from fgms_b200 import backend
     p = Problem(_sub_map(3000, 20, 31), c_in, c_out, seed=9, mode="fp16")
-    assert backend.kernel_family("wgrad", c_in, c_out, torch.float16) == "tcgen05"
+    assert backend.kernel_family("wgrad", c_in, c_out, torch.float16, True, p.km.k_vol) == "tcgen05"
     ref = p.ref_wgrad()
     prior = (torch.randn_like(p.weights) * 0.5)
     for fp32_sums in (False, True):
@@ -188,3 +206,40 @@ def test_fp16_wgrad_both_forms(c_in, c_out):
         finally:
             backend.WGRAD_FP32_SUMS = False
         assert err(w_grad, ref) <= TOL["fp16"]
+
+
+@pytest.mark.parametrize("mode", MODES)
+def test_kpos_beyond_the_maps_is_clamped_and_counted(mode):
+    """A stale kpos that points past the end of the maps must not move a read past them: the kernels clamp
+    every entry to the maps' length, count the problem, and compute the pairs that do exist."""
+    from fgms_b200 import backend
+    from oracle import spconv_oracle as orc
+    p = Problem(_sub_map(800, 11, 12), 64, 64, seed=3, mode=mode)
+    k_vol, pairs = p.km.k_vol, p.km.pairs
+    cut = int(p.km.kpos[k_vol - 2])             # the maps passed hold only the first `cut` pairs
+    p.imap, p.omap = p.imap[:cut].contiguous(), p.omap[:cut].contiguous()
+    assert cut < pairs
+    backend.device_status(reset=True)
+    out = p.run_fwd()
+    in_grad, w_grad = p.run_bwd()
+    assert backend.device_status() >= 3          # one report per launch at least
+    kpos = np.minimum(p.km.kpos, cut).astype(np.int32)
+    assert err(out, orc.fwd(p.f_np, p.w_np, p.km.n_out, kpos, p.km.imap[:cut], p.km.omap[:cut])) <= TOL[mode]
+    assert err(in_grad, orc.dgrad(p.g_np, p.w_np, p.km.n_in, kpos, p.km.imap[:cut], p.km.omap[:cut])) <= TOL[mode]
+    assert err(w_grad, orc.wgrad(p.f_np, p.g_np, k_vol, kpos, p.km.imap[:cut], p.km.omap[:cut])) <= TOL[mode]
+
+
+def test_unaligned_tensors_fall_back_and_are_counted():
+    """Tensors that are not 16-byte aligned cannot feed the tensor-core kernels: the CUDA-core kernels run
+    instead, the result is still right, and the fallback counter says so."""
+    from fgms_b200 import backend
+    p = Problem(_sub_map(700, 10, 5), 64, 64, seed=6, mode="fp16")
+    storage = torch.zeros(p.feats.numel() + 8, dtype=p.dtype, device="cuda")
+    shifted = storage[1:1 + p.feats.numel()].view_as(p.feats)  # 2 bytes off a 16-byte boundary
+    shifted.copy_(p.feats)
+    assert shifted.data_ptr() % 16 != 0
+    p.feats = shifted
+    before = backend.fallback_count()
+    out = p.run_fwd()
+    assert backend.fallback_count() == before + 1
+    assert err(out, p.ref_fwd()) <= TOL["fp16"]
