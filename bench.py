@@ -304,15 +304,15 @@ def run_cfg5(args, dev, rank, world, flush):
         # per-layer table and the roofline of the slowest call (eager launches with events around every call)
         hbm, f16_peak, _ = load_peaks()
         rows = step.profile(reps=5, flush=flush)
-        by_name = {l.name: (i, l) for i, l in enumerate(spec)}
+        by_name = {l.name: (l, step.run_spec[i]) for i, l in enumerate(spec)}
         table, worst = [], None
         for r in rows:
-            i, l = by_name[r["layer"]]
+            l, run_l = by_name[r["layer"]]  # as specified (flops and bytes count the real channels) and as run
             pairs = int(umaps.of(l).pairs)
             b = workloads.layer_bytes(pairs, l.c_in, l.c_out, l.k_vol, 2, r["pass"])
             fl = 2.0 * pairs * l.c_in * l.c_out
             t_roof = max(b / (hbm * 1e9), fl / (f16_peak * 1e12)) * 1e3
-            fam = backend.kernel_family(r["pass"], l.c_in, l.c_out, torch.float16, True, l.k_vol)
+            fam = backend.kernel_family(r["pass"], run_l.c_in, run_l.c_out, torch.float16, True, l.k_vol)
             row = {"layer": l.name, "pass": r["pass"], "shape": f"{l.c_in}->{l.c_out} k{l.k_vol}", "pairs": pairs,
                    "ms": round(r["ms"], 5), "frac": round(t_roof / r["ms"], 4), "family": fam}
             table.append(row)

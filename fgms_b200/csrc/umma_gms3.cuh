@@ -117,7 +117,9 @@ __device__ __forceinline__ G3Tile g3_tile(const G3Walk& w, const GmsParams& p, c
 // the weight matrix of the walk's tile (needs no table access)
 __device__ __forceinline__ int g3_widx(const G3Walk& w, const GmsParams& p) { return w.seg == p.k_vol ? p.dense_weight : w.seg; }
 
-template <bool TF32, bool TRANS_W>
+// FULL: both row lengths are whole 128-byte spans (the large-channel layers).  Every per-chunk guard below is
+// then a compile-time constant; the hot loops of that instantiation carry no test the short-row shapes need.
+template <bool TF32, bool TRANS_W, bool FULL>
 __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G3Config cfg) {
   using namespace umma;
   constexpr int ES = TF32 ? 4 : 2;
@@ -186,8 +188,8 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     // `lpr` lanes share a row, one 16-byte chunk each: 8 for rows of a whole span or more, 4 / 2 for 64- /
     // 32-byte rows, so that short rows still keep every lane busy.  This thread copies chunk pc of the rows
     // 16 pw + rsub + rpp j, j < n_pass.
-    const int lpr = k_bytes > 64 ? 8 : (k_bytes > 32 ? 4 : 2);
-    const int rpp = 32 / lpr, n_pass = 16 / rpp;  // rows per warp-wide copy: 4 / 8 / 16; copies per tile: 4 / 2 / 1
+    const int lpr = (FULL || k_bytes > 64) ? 8 : (k_bytes > 32 ? 4 : 2);
+    const int rpp = 32 / lpr, n_pass = FULL ? 4 : 16 / rpp;  // rows per warp-wide copy: 4 / 8 / 16; copies per tile: 4 / 2 / 1
     const int pc = lane % lpr, rsub = lane / lpr;
     const uint8_t* src = static_cast<const uint8_t*>(p.src);
     const uint8_t* wts = static_cast<const uint8_t*>(p.weights);
@@ -281,17 +283,17 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int g = __shfl_sync(0xffffffffu, ev, (rsub + rpp * j) & 15);
-        valid[j] = g >= 0 && j < n_pass;
+        valid[j] = g >= 0 && (FULL || j < n_pass);
         rsrc[j] = src + (size_t)max(g, 0) * src_row_bytes + (size_t)pc * 16;
       }
       for (int kc = 0; kc < kch && ok; ++kc) {
         ok = g3_wait(&sh->empty[s], ph ^ 1u, abort_flag);
         if (!ok) break;
         const uint32_t st = smem_u32(sStage + (size_t)s * G3_STAGE_BYTES);
-        if (kc * 128 + pc * 16 < k_bytes) {  // the last chunk of a row that is no whole number of spans is partly filled
+        if (FULL || kc * 128 + pc * 16 < k_bytes) {  // the last chunk of a row that is no whole number of spans is partly filled
 #pragma unroll
           for (int j = 0; j < 4; ++j)
-            if (j < n_pass) cp_async16(st + a_dst[j], rsrc[j] + (size_t)kc * 128, valid[j]);
+            if (FULL || j < n_pass) cp_async16(st + a_dst[j], rsrc[j] + (size_t)kc * 128, valid[j]);
         }
         // the stage's barrier hears from this thread when everything it has issued so far has landed
         cp_async_arrive_noinc(smem_u32(&sh->full[s]));
@@ -330,10 +332,10 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
           fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
           tc_fence_after();
           const uint32_t sa = smem_u32(sStage + (size_t)s * G3_STAGE_BYTES);
-          const int n_ks = min(4, (k_bytes - kc * 128) >> 5);  // 32-byte MMA steps this chunk holds
+          const int n_ks = FULL ? 4 : min(4, (k_bytes - kc * 128) >> 5);  // 32-byte MMA steps this chunk holds
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
-            if (ks >= n_ks) break;
+            if (!FULL && ks >= n_ks) break;
             const uint64_t a_desc = make_sdesc(sa + ks * 32u, 16u, 1024u);
             uint64_t b_desc;
             if (!TRANS_W) {
@@ -413,8 +415,8 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
         const uint32_t taddr = tmem_base + ((uint32_t)(q4 * 32) << 16) + (uint32_t)(buf * cfg.n_acc);
         for (uint32_t cb = 0; cb < row_bytes; cb += 128) {
           // bytes of this block that belong to the row; `lpe` lanes share a row in the reds below
-          const uint32_t vb = min(128u, row_bytes - cb);
-          const uint32_t lpe = vb > 64 ? 8u : (vb > 32 ? 4u : 2u), rpe = 32u / lpe;
+          const uint32_t vb = FULL ? 128u : min(128u, row_bytes - cb);
+          const uint32_t lpe = (FULL || vb > 64) ? 8u : (vb > 32 ? 4u : 2u), rpe = 32u / lpe;
           const uint32_t ch = (uint32_t)lane % lpe, rsub = (uint32_t)lane / lpe;  // red: chunk ch of rows rsub + rpe u
           const uint32_t col0 = cb / ES;
 #pragma unroll
@@ -450,10 +452,10 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
           }
           __syncwarp();
           uint8_t* dcol = dst + cb + (ch << 4);
-          const bool ch_ok = (ch << 4) < vb;
+          const bool ch_ok = FULL || (ch << 4) < vb;
 #pragma unroll
           for (uint32_t u = 0; u < 8; ++u) {
-            if (u >= lpe) break;  // 32 rows = lpe passes of rpe rows
+            if (!FULL && u >= lpe) break;  // 32 rows = lpe passes of rpe rows
             const uint32_t r = rsub + rpe * u;
             const int sr = __shfl_sync(0xffffffffu, srow, r);
             const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
@@ -514,11 +516,17 @@ inline int ensure_smem(K kernel, int bytes, std::atomic<int>* granted /* [64], b
   return 0;
 }
 
+template <bool TF32, bool TRANS_W, bool FULL>
+inline int g3_launch_as(const GmsParams& p, const G3Config& cfg, cudaStream_t st, int sms, int max_smem) {
+  static std::atomic<int> granted[64];
+  if (int rc = ensure_smem(umma_gms3_kernel<TF32, TRANS_W, FULL>, max_smem, granted)) return rc;
+  return launch_pdl(umma_gms3_kernel<TF32, TRANS_W, FULL>, sms, G3_THREADS, (size_t)cfg.smem, st, p, cfg) == cudaSuccess ? 0 : -1;
+}
 template <bool TF32, bool TRANS_W>
 inline int g3_launch(const GmsParams& p, const G3Config& cfg, cudaStream_t st, int sms, int max_smem) {
-  static std::atomic<int> granted[64];
-  if (int rc = ensure_smem(umma_gms3_kernel<TF32, TRANS_W>, max_smem, granted)) return rc;
-  return launch_pdl(umma_gms3_kernel<TF32, TRANS_W>, sms, G3_THREADS, (size_t)cfg.smem, st, p, cfg) == cudaSuccess ? 0 : -1;
+  const int es = TF32 ? 4 : 2;
+  const bool full = (p.c_in * es) % 128 == 0 && (p.c_out * es) % 128 == 0;
+  return full ? g3_launch_as<TF32, TRANS_W, true>(p, cfg, st, sms, max_smem) : g3_launch_as<TF32, TRANS_W, false>(p, cfg, st, sms, max_smem);
 }
 
 // 0 launched, 1 the pointers are not 16-byte aligned or the shape has no plan (the caller takes the CUDA-core

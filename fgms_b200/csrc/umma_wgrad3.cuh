@@ -70,7 +70,8 @@ __device__ __forceinline__ void w3_stage(const G3Walk& w, int pb, const int* kpo
   *cnt = min(pb, kpos_s[w.seg + 1] - seg_base - lt * pb);
 }
 
-template <bool TF32>
+// FULL: both row lengths are whole 128-byte pieces; the producers' copy loops then carry no per-chunk test.
+template <bool TF32, bool FULL>
 __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams p, W3Config cfg) {
   using namespace umma;
   constexpr int ES = TF32 ? 4 : 2;
@@ -134,7 +135,10 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
     const uint8_t* og = static_cast<const uint8_t*>(p.out_grad);
     const uint32_t a_row_bytes = (uint32_t)p.c_in * ES, b_row_bytes = (uint32_t)p.c_out * ES;
-    const int nha = (int)(a_row_bytes + 127) / 128, nhb = (int)(b_row_bytes + 127) / 128;  // 128-byte pieces per row: 1 .. 8
+    // 128-byte pieces of a row this lane's 16-byte chunk exists in (the last piece of a row that is no whole
+    // number of pieces is filled in part): 0 .. 8
+    const int nha = FULL ? (int)a_row_bytes / 128 : ((int)a_row_bytes - (lane & 7) * 16 + 127) / 128;
+    const int nhb = FULL ? (int)b_row_bytes / 128 : ((int)b_row_bytes - (lane & 7) * 16 + 127) / 128;
     // Lane (rs, c) = (lane / 8, lane % 8) copies 16-byte chunk c of every 128-byte piece of the rows
     // rs, rs + 4, ... of the warp's block: one shuffle and one address per row, then one cp.async per
     // piece at a fixed distance (128 bytes in global memory, `lbo` in shared memory).
@@ -197,13 +201,12 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
           const uint8_t* pa = feats_c + (size_t)max(ia, 0) * a_row_bytes;
           const uint8_t* pb_ = og_c + (size_t)max(ib, 0) * b_row_bytes;
           const uint32_t da = sa + dst_rel[u], db = sb + dst_rel[u];
-          // (the last piece of a row that is no whole number of pieces is filled in part)
 #pragma unroll
           for (int h = 0; h < 8; ++h)
-            if (h < nha && (uint32_t)(h * 128 + cc * 16) < a_row_bytes) cp_async16_n(da + (uint32_t)h * lbo, pa + h * 128, na);
+            if (h < nha) cp_async16_n(da + (uint32_t)h * lbo, pa + h * 128, na);
 #pragma unroll
           for (int h = 0; h < 8; ++h)
-            if (h < nhb && (uint32_t)(h * 128 + cc * 16) < b_row_bytes) cp_async16_n(db + (uint32_t)h * lbo, pb_ + h * 128, nb);
+            if (h < nhb) cp_async16_n(db + (uint32_t)h * lbo, pb_ + h * 128, nb);
         }
       }
       // the stage's barrier hears from this thread when everything it has issued so far has landed
@@ -395,11 +398,17 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   return true;
 }
 
+template <bool TF32, bool FULL>
+inline int w3_launch_as(const WgradParams& p, const W3Config& cfg, cudaStream_t st, int sms, int max_smem) {
+  static std::atomic<int> granted[64];
+  if (int rc = ensure_smem(umma_wgrad3_kernel<TF32, FULL>, max_smem, granted)) return rc;
+  return launch_pdl(umma_wgrad3_kernel<TF32, FULL>, sms, W3_THREADS, (size_t)cfg.smem, st, p, cfg) == cudaSuccess ? 0 : -1;
+}
 template <bool TF32>
 inline int w3_launch(const WgradParams& p, const W3Config& cfg, cudaStream_t st, int sms, int max_smem) {
-  static std::atomic<int> granted[64];
-  if (int rc = ensure_smem(umma_wgrad3_kernel<TF32>, max_smem, granted)) return rc;
-  return launch_pdl(umma_wgrad3_kernel<TF32>, sms, W3_THREADS, (size_t)cfg.smem, st, p, cfg) == cudaSuccess ? 0 : -1;
+  const int es = TF32 ? 4 : 2;
+  const bool full = (p.c_in * es) % 128 == 0 && (p.c_out * es) % 128 == 0;
+  return full ? w3_launch_as<TF32, true>(p, cfg, st, sms, max_smem) : w3_launch_as<TF32, false>(p, cfg, st, sms, max_smem);
 }
 
 // 0 launched, 1 the pointers are not 16-byte aligned or the shape has no plan (the caller takes the CUDA-core

@@ -154,6 +154,11 @@ class UNetStep:
     ``feats`` ``[n0, c_in]`` and ``grad_out`` ``[n0, widths[0]]`` are the step's inputs; after ``run()`` the flat
     fp16 ``w_grad`` holds every layer's weight gradient (``w_grads[i]`` is the view of layer i), summed over
     the ranks of ``group`` when there are several.  The first layer's input gradient is not computed.
+
+    The stem's few input channels (4) are padded with zero channels to 16 inside the step: 8-byte rows cannot be
+    gathered in 16-byte pieces and would run on the CUDA-core kernels, 32-byte rows run on the tensor cores.  The
+    padded weight rows multiply zeros and their gradient is zero; ``weights[0]`` / ``w_grads[0]`` show the real
+    ``c_in`` rows only.  ``set_input`` refreshes the padded copy when the caller's features change.
     """
 
     def __init__(self, spec, umaps: UNetMaps, weights, feats, grad_out, group=None, bucket_bytes: int = 6 << 20,
@@ -163,6 +168,13 @@ class UNetStep:
         from .dist import world_size
         self.spec, self.umaps, self.group = list(spec), umaps, group
         self.device = feats.device
+        # the layers as they are run: the stem with its input channels padded to a multiple of 16
+        from dataclasses import replace
+        self._cin0 = self.spec[0].c_in
+        run_spec = list(self.spec)
+        if self._cin0 % 16:
+            run_spec[0] = replace(run_spec[0], c_in=(self._cin0 + 15) // 16 * 16)
+        report_spec, self.spec = self.spec, run_spec
         # exchange: None = the data-parallel form (fp32 sums in buckets, all-reduced, added to w_grad at the end)
         # when the process group has several ranks; False = this rank alone, whatever the group; True = the
         # data-parallel form even with one rank (the collective is then skipped)
@@ -189,7 +201,12 @@ class UNetStep:
         total = sum(pad(sizes[n]) for n in names)
         self._act_flat = torch.zeros(total, dtype=dt, device=dev)
         self._grad_flat = torch.zeros(total, dtype=dt, device=dev)
-        self.val, self.grad = {"input": feats}, {}
+        if run_spec[0].c_in != self._cin0:
+            self._input = torch.zeros((feats.size(0), run_spec[0].c_in), dtype=dt, device=dev)
+            self._input[:, : self._cin0].copy_(feats)
+        else:
+            self._input = feats
+        self.val, self.grad = {"input": self._input}, {}
         off = 0
         for n in names:
             shape = (n_vox[level[n]], width[n])
@@ -214,7 +231,8 @@ class UNetStep:
             n = l.k_vol * l.c_in * l.c_out
             shape = (l.k_vol, l.c_in, l.c_out)
             self.weights[i] = self._w_flat[off: off + n].view(shape)
-            self.weights[i].copy_(torch.as_tensor(weights[i]).to(dev, dt))
+            w_src = torch.as_tensor(weights[i]).to(dev, dt)
+            self.weights[i][:, : w_src.size(1), :].copy_(w_src)  # (padded input channels keep zero weights)
             self.w_grads[i] = self.w_grad[off: off + n].view(shape)
             if self.multi:
                 self._dw32_views[i] = self._dw32[off: off + n]
@@ -263,6 +281,17 @@ class UNetStep:
                 wgrad[14], wgrad[15] = self._ws.data_ptr(), self._ws.numel() * 4
         self._bucket_end = {last: (lo, hi) for lo, hi, last in self.buckets}
         self.launches_per_step = len(self.spec) * 3 - 1
+        # what the caller sees: the layer list as given, the stem's real input channels only
+        self.run_spec, self.spec = self.spec, report_spec
+        self._w_run = list(self.weights)
+        self.weights[0] = self.weights[0][:, : self._cin0, :]
+        self.w_grads[0] = self.w_grads[0][:, : self._cin0, :]
+
+    def set_input(self, feats):
+        """Copy new input features ``[n0, c_in]`` into the step's (channel-padded) input buffer."""
+        if self._input is feats:
+            return
+        self._input[:, : self._cin0].copy_(feats)
 
     def _stream(self):
         import torch
