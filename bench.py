@@ -424,6 +424,48 @@ def run_row_shard(args, dev, rank, world, wl, p, flush):
             "rows_outside_own_range_zero": outside_zero, "rel_err_vs_uncut": errs, "ok": bool(flag.item() > 0)}
 
 
+def run_reference_cuda(wl, p, prepare, ev):
+    """The reference's CUDA extension (built from its two source files for sm_100a by ``oracle/build_ref.py``) timed on
+    this workload's tensors with the same events and L2 flush.  Only fp16 layers whose channel counts are multiples of
+    32 and whose output width is not 64 are run: the reference's other kernels for the benchmark shapes read or write
+    out of range (see the header of tests/test_gpu_reference_cuda.py)."""
+    import torch
+    from oracle import build_ref
+    if not build_ref.available():
+        return {"unavailable": "the reference extension is not built (python -m oracle.build_ref needs a checkout of the reference)"}
+    if not (wl.mode == "fp16" and wl.c_in % 32 == 0 and wl.c_out % 32 == 0 and wl.c_out != 64 and wl.c_in > 16):
+        return {"unavailable": f"the reference's kernels for {wl.mode} {wl.c_in}->{wl.c_out} are not sound; not launched"}
+    ref = build_ref.load()
+    km = wl.kmap
+    out = torch.zeros((km.n_out, wl.c_out), dtype=p.dtype, device=p.feats.device)
+    in_grad = torch.zeros((km.n_in, wl.c_in), dtype=p.dtype, device=p.feats.device)
+    w_grad = torch.zeros_like(p.weights)
+
+    def step():
+        ref.fgms_fusion_fwd_cuda(p.feats, p.weights, p.qsum, out, p.kpos, p.qkpos, p.imap, p.omap, False, True)
+        ref.fgms_bwd_cuda(p.grad_out, p.feats, p.weights, p.qsum, in_grad, w_grad, p.kpos, p.qkpos, p.imap, p.omap, False, True)
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize()
+    fwd_ms, step_ms = [], []
+    for _ in range(20):
+        prepare(); out.zero_(); in_grad.zero_(); w_grad.zero_()
+        a, b, c = ev(), ev(), ev()
+        a.record()
+        ref.fgms_fusion_fwd_cuda(p.feats, p.weights, p.qsum, out, p.kpos, p.qkpos, p.imap, p.omap, False, True)
+        b.record()
+        ref.fgms_bwd_cuda(p.grad_out, p.feats, p.weights, p.qsum, in_grad, w_grad, p.kpos, p.qkpos, p.imap, p.omap, False, True)
+        c.record()
+        torch.cuda.synchronize()
+        fwd_ms.append(a.elapsed_time(b)); step_ms.append(a.elapsed_time(c))
+    fm, sm = statistics.mean(fwd_ms), statistics.mean(step_ms)
+    from fgms_b200 import workloads
+    return {"what": "hkeee21/FGMS CUDA extension compiled for sm_100a (wmma kernels), same tensors, events and L2 flush; "
+                    "fused forward + backward (dgrad + wgrad) through its own Python functions",
+            "fwd_ms": fm, "bwd_ms": sm - fm, "step_ms": sm, "value": workloads.flops(wl) / (sm * 1e-3) / 1e12, "unit": UNIT}
+
+
 def run_ours(args):
     import numpy as np
     import torch
@@ -553,24 +595,20 @@ def run_ours(args):
         barrier()
         alone_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
 
-    # per-pass durations (for the roofline of the slowest pass): kernels alone, events between the passes
-    pe = []
-    for _ in range(min(args.steps, 50)):
-        prepare()
-        e = [ev() for _ in range(4)]
-        e[0].record()
-        layer.forward(p.feats, p.weights, out)
-        e[1].record()
-        backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
-        e[2].record()
-        wgrad_kernel_only()
-        e[3].record()
-        pe.append(e)
-    barrier()
-    for e in pe:
-        pass_ms["fwd"].append(e[0].elapsed_time(e[1]))
-        pass_ms["dgrad"].append(e[1].elapsed_time(e[2]))
-        pass_ms["wgrad"].append(e[2].elapsed_time(e[3]))
+    # per-pass durations (for the roofline of the slowest pass): each kernel alone between two events, right after
+    # the untimed L2 flush (the host has enqueued the call long before the flush ends, so no launch gap is timed)
+    calls = {"fwd": lambda: layer.forward(p.feats, p.weights, out),
+             "dgrad": lambda: backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80),
+             "wgrad": wgrad_kernel_only}
+    for name, call in calls.items():
+        pe = []
+        for _ in range(min(args.steps, 50)):
+            prepare()
+            a, b = ev(), ev()
+            a.record(); call(); b.record()
+            pe.append((a, b))
+        barrier()
+        pass_ms[name] = [a.elapsed_time(b) for a, b in pe]
 
     # warm-L2 variant (no flush), reported beside the headline
     for _ in range(2):
@@ -690,6 +728,11 @@ def run_ours(args):
                        "identical_to_host_builder": same,
                        "note": "includes the allocation of its outputs and one stream synchronisation (pair count)"}
 
+    # ---- the reference's own CUDA kernels on the same tensors (only where they are sound, only when built) ------
+    reference_cuda = None
+    if rank == 0 and args.reference_cuda:
+        reference_cuda = run_reference_cuda(wl, p, prepare, ev)
+
     fallbacks = backend.fallback_count() - fallbacks0
     strong = run_row_shard(args, dev, rank, world, wl, p, flush) if shard_rows else None
     cfg5, cfg5_check = (None, None)
@@ -754,6 +797,10 @@ def run_ours(args):
             line["pass_ms"]["step_kernels_only"] = alone_ms
             line["pass_ms"]["allreduce_exposed"] = total_ms / k - alone_ms
             line["multi_gpu_check"] = check
+        if reference_cuda is not None:
+            if "step_ms" in reference_cuda:
+                reference_cuda["speedup_of_this_library"] = reference_cuda["step_ms"] / (total_ms / k)
+            line["reference_cuda"] = reference_cuda
         if strong is not None:
             line["strong_scaling"] = strong
         if cfg5 is not None:
@@ -788,6 +835,8 @@ def main():
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the eager step instead of a CUDA-graph replay of it")
     ap.add_argument("--no-cfg5", dest="cfg5", action="store_false", help="skip the encoder-decoder stack")
     ap.add_argument("--cfg5-steps", type=int, default=20)
+    ap.add_argument("--no-reference-cuda", dest="reference_cuda", action="store_false",
+                    help="do not time the reference's CUDA kernels beside this library (they run only when built and sound)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

@@ -419,29 +419,23 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
           const uint32_t lpe = (FULL || vb > 64) ? 8u : (vb > 32 ? 4u : 2u), rpe = 32u / lpe;
           const uint32_t ch = (uint32_t)lane % lpe, rsub = (uint32_t)lane / lpe;  // red: chunk ch of rows rsub + rpe u
           const uint32_t col0 = cb / ES;
+          // 16 accumulator columns at a time: few registers in flight (a warp scheduler holding five warps of this
+          // CTA leaves each thread about a hundred)
 #pragma unroll
-          for (uint32_t c0 = 0; c0 < BLK_COLS; c0 += 32) {
-            uint32_t v0[16], v1[16];
-            tmem_ld16(taddr + col0 + c0, v0);
-            tmem_ld16(taddr + col0 + c0 + 16, v1);
+          for (uint32_t c0 = 0; c0 < BLK_COLS; c0 += 16) {
+            uint32_t v[16];
+            tmem_ld16(taddr + col0 + c0, v);
             tmem_ld_wait();
             if (TF32) {
 #pragma unroll
-              for (int k = 0; k < 4; ++k) {
-                *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)k ^ sw7) << 4)) = make_uint4(v0[4 * k], v0[4 * k + 1], v0[4 * k + 2], v0[4 * k + 3]);
-                *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)(4 + k) ^ sw7) << 4)) = make_uint4(v1[4 * k], v1[4 * k + 1], v1[4 * k + 2], v1[4 * k + 3]);
-              }
-            } else {
-              const uint32_t ch0 = c0 / 8;
-              uint32_t h[16];
-#pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                h[k] = pack_half2(__uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
-                h[8 + k] = pack_half2(__uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
-              }
-#pragma unroll
               for (int k = 0; k < 4; ++k)
-                *reinterpret_cast<uint4*>(patch + lane * 128 + (((ch0 + k) ^ sw7) << 4)) = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+                *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)(c0 / 4 + k) ^ sw7) << 4)) = make_uint4(v[4 * k], v[4 * k + 1], v[4 * k + 2], v[4 * k + 3]);
+            } else {
+              uint32_t h[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) h[k] = pack_half2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
+              *reinterpret_cast<uint4*>(patch + lane * 128 + (((c0 / 8) ^ sw7) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+              *reinterpret_cast<uint4*>(patch + lane * 128 + (((c0 / 8 + 1) ^ sw7) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
             }
           }
           if (cb + 128 >= row_bytes) {

@@ -295,19 +295,14 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
           const bool m128 = mt + 1 < cfg.n_mtile || cfg.last_m == 128;
           for (int c0 = 0; c0 < p.c_out; c0 += 64) {
 #pragma unroll
-            for (int half_i = 0; half_i < 2; ++half_i) {
-              uint32_t v0[16], v1[16], h[16];
-              tmem_ld16(taddr + c0 + 32 * half_i, v0);
-              tmem_ld16(taddr + c0 + 32 * half_i + 16, v1);
+            for (int q = 0; q < 4; ++q) {  // 16 columns at a time: few registers in flight
+              uint32_t v[16], h[8];
+              tmem_ld16(taddr + c0 + 16 * q, v);
               tmem_ld_wait();
 #pragma unroll
-              for (int k = 0; k < 8; ++k) {
-                h[k] = pack_half2(__uint_as_float(v0[2 * k]), __uint_as_float(v0[2 * k + 1]));
-                h[8 + k] = pack_half2(__uint_as_float(v1[2 * k]), __uint_as_float(v1[2 * k + 1]));
-              }
-#pragma unroll
-              for (int k = 0; k < 4; ++k)
-                *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)(4 * half_i + k) ^ sw7) << 4)) = make_uint4(h[4 * k], h[4 * k + 1], h[4 * k + 2], h[4 * k + 3]);
+              for (int k = 0; k < 8; ++k) h[k] = pack_half2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
+              *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)(2 * q) ^ sw7) << 4)) = make_uint4(h[0], h[1], h[2], h[3]);
+              *reinterpret_cast<uint4*>(patch + lane * 128 + (((uint32_t)(2 * q + 1) ^ sw7) << 4)) = make_uint4(h[4], h[5], h[6], h[7]);
             }
             __syncwarp();
 #pragma unroll
