@@ -506,7 +506,8 @@ def run_ours(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     pass_ms = {"fwd": [], "dgrad": [], "wgrad": []}
 
-    bound = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80) if world > 1 else None
+    bound = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80,
+                            transport=args.transport) if world > 1 else None
     bound_alone = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80,
                                   exchange=False) if world > 1 else None
     ws = backend.wgrad_workspace(wl.c_in, wl.c_out, km.k_vol, dev) if p.dtype == torch.float16 else None
@@ -797,6 +798,9 @@ def run_ours(args):
             line["pass_ms"]["step_kernels_only"] = alone_ms
             line["pass_ms"]["allreduce_exposed"] = total_ms / k - alone_ms
             line["multi_gpu_check"] = check
+            line["exchange"] = {"peer": "fgms_b200_peer_exchange: one kernel per rank over peer-mapped memory (plain loads and stores), on a "
+                                        "side stream beside the input-gradient kernel",
+                                "nccl": "NCCL all-reduce of the fp32 sums (async, beside the input-gradient kernel)"}[args.transport]
         if reference_cuda is not None:
             if "step_ms" in reference_cuda:
                 reference_cuda["speedup_of_this_library"] = reference_cuda["step_ms"] / (total_ms / k)
@@ -835,6 +839,8 @@ def main():
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the eager step instead of a CUDA-graph replay of it")
     ap.add_argument("--no-cfg5", dest="cfg5", action="store_false", help="skip the encoder-decoder stack")
     ap.add_argument("--cfg5-steps", type=int, default=20)
+    ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
+                    help="N > 1: how the weight-gradient sums are exchanged: the library's kernel over peer memory, or an NCCL all-reduce")
     ap.add_argument("--no-reference-cuda", dest="reference_cuda", action="store_false",
                     help="do not time the reference's CUDA kernels beside this library (they run only when built and sound)")
     args = ap.parse_args()

@@ -34,6 +34,8 @@ SIGNATURES = {
                                             c_size_t, c_void_p, c_void_p]),
     "fgms_b200_transpose_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_size_t, c_void_p]),
+    "fgms_b200_peer_exchange_flag_bytes": (c_size_t, [c_int]),
+    "fgms_b200_peer_exchange": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, ctypes.c_uint32, c_int64, c_int, c_void_p]),
     "fgms_b200_kernel_family": (c_int, [c_int] * 6),
     "fgms_b200_fallback_count": (c_int64, []),
     "fgms_b200_device_status": (c_int64, [c_int]),

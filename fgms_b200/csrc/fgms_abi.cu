@@ -16,6 +16,7 @@
 #include "map_builder.cuh"
 #include "umma_gms3.cuh"
 #include "umma_wgrad3.cuh"
+#include "peer_exchange.cuh"
 
 namespace {
 
@@ -515,6 +516,36 @@ int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const in
   if (!fgms::maps::finish(w.dense(), k_vol, n_in, w.tile_sums(), kpos_t, in_map_t, out_map_t, st)) return cuda_fail("map builder launch");
   g_launches += 5;
   return FGMS_OK;
+}
+
+// ---------------------------------------------------------------------------------------------
+// Sum of the ranks' weight-gradient partial sums over peer memory (csrc/peer_exchange.cuh)
+// ---------------------------------------------------------------------------------------------
+size_t fgms_b200_peer_exchange_flag_bytes(int world) {
+  if (world < 1 || world > fgms::PX_MAX_WORLD) return 0;
+  return (((size_t)(2 * world + 1) * sizeof(uint32_t)) + 255) & ~(size_t)255;
+}
+
+int fgms_b200_peer_exchange(const float* const* sums, float* const* reduced, uint32_t* const* flags, int rank,
+                            int world, int64_t count, uint32_t epoch, int64_t wait_limit_cycles, int ctas,
+                            void* stream) {
+  if (world < 1 || world > fgms::PX_MAX_WORLD) return fail(FGMS_ERR_INVALID_ARG, "world %d outside [1, %d]", world, fgms::PX_MAX_WORLD);
+  if (rank < 0 || rank >= world) return fail(FGMS_ERR_INVALID_ARG, "rank %d outside [0, %d)", rank, world);
+  if (count < 0 || count % 4 != 0) return fail(FGMS_ERR_INVALID_ARG, "count must be a non-negative multiple of 4");
+  if (!sums || !reduced || !flags) return fail(FGMS_ERR_INVALID_ARG, "null pointer table");
+  if (ctas < 1 || ctas > 1024) return fail(FGMS_ERR_INVALID_ARG, "ctas %d outside [1, 1024]", ctas);
+  if (wait_limit_cycles < 0) return fail(FGMS_ERR_INVALID_ARG, "negative wait limit");
+  fgms::PeerExchangeParams p = {};
+  for (int q = 0; q < world; ++q) {
+    if (!flags[q] || (count > 0 && (!sums[q] || !reduced[q]))) return fail(FGMS_ERR_INVALID_ARG, "null buffer of rank %d", q);
+    if ((reinterpret_cast<uintptr_t>(sums[q]) | reinterpret_cast<uintptr_t>(reduced[q])) & 15)
+      return fail(FGMS_ERR_INVALID_ARG, "buffers of rank %d are not 16-byte aligned", q);
+    p.sums[q] = sums[q]; p.reduced[q] = reduced[q]; p.flags[q] = flags[q];
+  }
+  p.count = count; p.epoch = epoch; p.rank = rank; p.world = world;
+  p.wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : fgms::PX_WAIT_LIMIT_CYCLES;
+  fgms::peer_exchange_kernel<<<ctas, fgms::PX_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
+  return check_launch("peer_exchange_kernel");
 }
 
 int64_t fgms_b200_device_status(int reset) {

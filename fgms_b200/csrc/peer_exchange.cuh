@@ -1,0 +1,115 @@
+// Sum of the ranks' fp32 weight-gradient partial sums over peer memory (NVLink / NVSwitch), as one small kernel
+// per rank that runs beside the input-gradient kernel.
+//
+// Every rank holds three peer-mapped buffers of the same size: `sums` (its own fp32 partial sums, written by its
+// weight-gradient kernel), `reduced` (receives the total) and a few flag words.  The element range is cut into
+// `world` slices; rank r owns slice r.  One call, on every rank:
+//
+//   1. announce   a thread stores this call's epoch into flag A[rank] of every rank (after a system-scope fence:
+//                 the weight-gradient kernel before this one in the stream has finished, its sums are visible);
+//   2. wait       until A[p] >= epoch for every p in this rank's own flags;
+//   3. reduce     the rank's slice: load it from every rank's `sums` (plain peer loads, fixed order p = 0 .. world-1,
+//                 so the total is the same bits on every run), add, store the total into every rank's `reduced`;
+//   4. announce   the last CTA to finish stores the epoch into flag D[rank] of every rank;
+//   5. wait       until D[p] >= epoch for every p: this rank's `reduced` is complete and no peer still reads its `sums`.
+//
+// The reference has no multi-GPU path (backend/spconv.cu has no collective); this replaces the NCCL all-reduce of
+// the data-parallel step where its launch needs SMs the input-gradient kernel holds.  Only plain loads and stores
+// cross the link: no multicast, no atomics on peer memory.  Every wait is bounded; one that runs out is counted
+// (g_device_problems), the kernel returns, and the totals of that call are incomplete.  Epochs only grow, so flags
+// are never cleared.
+#pragma once
+
+#include "common.cuh"
+
+namespace fgms {
+
+constexpr int PX_MAX_WORLD = 16;
+constexpr int PX_THREADS = 128;  // small CTAs of few registers: they find room on SMs that a persistent kernel occupies
+constexpr long long PX_WAIT_LIMIT_CYCLES = 2000000000ll;  // about one second of SM clock
+
+struct PeerExchangeParams {
+  const float* sums[PX_MAX_WORLD];   // every rank's partial sums (index = rank)
+  float* reduced[PX_MAX_WORLD];      // every rank's buffer for the totals
+  uint32_t* flags[PX_MAX_WORLD];     // every rank's flag words: A[0 .. world), D[world .. 2 world), then one CTA counter
+  long long count;                   // fp32 values; a multiple of 4
+  long long wait_limit;              // cycles a wait may take
+  uint32_t epoch;                    // of this call: larger than that of any call before it
+  int rank, world;
+};
+
+__device__ __forceinline__ void px_store_flag(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t px_load_flag(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ float4 px_load4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void px_store4(float* p, float4 v) {
+  asm volatile("st.relaxed.sys.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(p), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+
+// Threads 0 .. world-1 of the CTA each watch one flag; the CTA learns whether all of them arrived in time.
+__device__ __forceinline__ bool px_wait_all(const uint32_t* my_flags, int world, uint32_t epoch, long long limit) {
+  __shared__ int timed_out;
+  if (threadIdx.x == 0) timed_out = 0;
+  __syncthreads();
+  if ((int)threadIdx.x < world) {
+    const long long start = clock64();
+    // epochs are compared by their distance so that the counter may wrap
+    while ((int32_t)(px_load_flag(my_flags + threadIdx.x) - epoch) < 0) {
+      if (clock64() - start > limit) { timed_out = 1; break; }
+      __nanosleep(64);
+    }
+  }
+  __syncthreads();
+  return timed_out == 0;
+}
+
+__global__ void __launch_bounds__(PX_THREADS) peer_exchange_kernel(PeerExchangeParams p) {
+  const int world = p.world, rank = p.rank;
+  uint32_t* mine = p.flags[rank];
+  if (blockIdx.x == 0 && (int)threadIdx.x < world) {
+    __threadfence_system();
+    px_store_flag(p.flags[threadIdx.x] + rank, p.epoch);
+  }
+  bool ok = px_wait_all(mine, world, p.epoch, p.wait_limit);
+  if (ok) {
+    const long long n4 = p.count / 4;
+    const long long lo = n4 * rank / world, hi = n4 * (rank + 1) / world;
+    for (long long i = lo + (long long)blockIdx.x * PX_THREADS + threadIdx.x; i < hi; i += (long long)gridDim.x * PX_THREADS) {
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int q0 = 0; q0 < world; q0 += 8) {  // eight peer loads in flight, added in rank order
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (q0 + u < world) v[u] = px_load4(p.sums[q0 + u] + 4 * i);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          if (q0 + u < world) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
+      }
+      for (int q = 0; q < world; ++q) px_store4(p.reduced[q] + 4 * i, acc);
+    }
+  }
+  // the last CTA of this rank to get here tells every rank that this rank's slice is written everywhere
+  __shared__ int last;
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const uint32_t done = atomicAdd(mine + 2 * world, 1u) + 1u;
+    __threadfence_system();  // what the other CTAs stored before they counted themselves is ordered before the flag below
+    last = (done % gridDim.x) == 0;  // the counter is never cleared: every call adds gridDim.x
+  }
+  __syncthreads();
+  if (last && (int)threadIdx.x < world) px_store_flag(p.flags[threadIdx.x] + world + rank, p.epoch);
+  if (ok) ok = px_wait_all(mine + world, world, p.epoch, p.wait_limit);
+  if (!ok && threadIdx.x == 0) report_problem();
+}
+
+}  // namespace fgms

@@ -22,7 +22,7 @@ import numpy as np
 from .maps import KernelMap
 
 __all__ = ["balanced_row_ranges", "shard_pairs_by_rows", "shard_map_device", "MapShard", "allreduce_sum_",
-           "SceneParallelLayer", "BoundSceneLayer"]
+           "SceneParallelLayer", "BoundSceneLayer", "PeerExchange"]
 
 
 def balanced_row_ranges(rows: np.ndarray, n_rows: int, world: int) -> np.ndarray:
@@ -119,6 +119,70 @@ def allreduce_sum_(tensor, group=None):
     return tensor
 
 
+class PeerExchange:
+    """Sum of every rank's fp32 partial sums over peer memory instead of an NCCL all-reduce
+    (``fgms_b200_peer_exchange``, ``csrc/peer_exchange.cuh``).
+
+    The ranks' buffers come from PyTorch's symmetric-memory allocator (one allocation per rank, mapped into every
+    process of ``group``); the library's kernel reads and writes them with plain loads and stores.  ``sums`` is
+    this rank's input (use it as the weight-gradient workspace), ``reduced`` receives the totals.  ``run()``
+    enqueues the kernel on ``stream`` — meant to be a side stream, so that the kernel (a few small CTAs) runs
+    beside the input-gradient kernel where NCCL's would wait for its SMs.
+
+    With one rank (or ``buffers`` given: pointer tables of an emulated group on one device, used by the tests)
+    no symmetric memory is involved.
+    """
+
+    def __init__(self, count: int, device, group=None, ctas: int = 32, wait_limit_cycles: int = 0, buffers=None):
+        import ctypes
+        import torch
+        from . import _lib
+        self._L, self._check = _lib.lib, _lib.check
+        self.device = torch.device(device)
+        self.count = (int(count) + 3) // 4 * 4
+        self.group = group
+        self.ctas, self.wait_limit, self.epoch = int(ctas), int(wait_limit_cycles), 0
+        if buffers is not None:
+            self.rank, self.world, sums, reduced, flags = buffers
+            self.sums, self.reduced = sums[self.rank], reduced[self.rank]
+            ptrs = ([t.data_ptr() for t in sums], [t.data_ptr() for t in reduced], [t.data_ptr() for t in flags])
+            self._keep = (sums, reduced, flags)
+        else:
+            self.world = world_size(group)
+            flag_bytes = self._L.fgms_b200_peer_exchange_flag_bytes(max(self.world, 1))
+            n_flag = flag_bytes // 4
+            total = 2 * self.count + n_flag
+            if self.world > 1:
+                import torch.distributed as dist
+                import torch.distributed._symmetric_memory as symm_mem
+                self.rank = dist.get_rank(group)
+                buf = symm_mem.empty(total, dtype=torch.float32, device=self.device)
+                buf.zero_()
+                handle = symm_mem.rendezvous(buf, group if group is not None else dist.group.WORLD)
+                torch.cuda.synchronize(self.device)
+                dist.barrier(group)  # every rank's flags are zero before anyone's first call
+                base = [int(p) for p in handle.buffer_ptrs]
+                self._keep = (buf, handle)
+            else:
+                self.rank = 0
+                buf = torch.zeros(total, dtype=torch.float32, device=self.device)
+                base = [buf.data_ptr()]
+                self._keep = (buf,)
+            self.sums, self.reduced = buf[: self.count], buf[self.count: 2 * self.count]
+            ptrs = (base, [b + 4 * self.count for b in base], [b + 8 * self.count for b in base])
+        arr = ctypes.c_void_p * self.world
+        self._tables = tuple(arr(*p) for p in ptrs)
+
+    def run(self, stream=None):
+        """Enqueue one exchange (every rank of the group must do the same); returns nothing."""
+        import torch
+        self.epoch += 1
+        st = (stream if stream is not None else torch.cuda.current_stream(self.device)).cuda_stream
+        with torch.cuda.device(self.device):
+            self._check(self._L.fgms_b200_peer_exchange(self._tables[0], self._tables[1], self._tables[2], self.rank, self.world,
+                                                        self.count, self.epoch, self.wait_limit, self.ctas, st))
+
+
 class SceneParallelLayer:
     """One sparse-convolution layer trained data-parallel: each rank its own scene.
 
@@ -176,7 +240,7 @@ class BoundSceneLayer:
     """
 
     def __init__(self, feats, weights, grad_out, out, in_grad, w_grad, kpos, imap, omap, arch80: bool, group=None,
-                 exchange: bool = True):
+                 exchange: bool = True, transport: str = "nccl"):
         import torch
         from . import _lib, backend
         k_vol = backend._common(feats, weights, kpos, imap, omap)
@@ -196,6 +260,11 @@ class BoundSceneLayer:
         # exchange = False keeps the multi-rank form of the step (fp32 sums, final addition) but skips the
         # all-reduce: the step's kernels alone, which is how the collective's exposed time is measured
         self.exchange = exchange and self.multi
+        # transport: "nccl" = all-reduce of the fp32 sums; "peer" = the library's own kernel over peer memory on a side
+        # stream (PeerExchange), which can run beside the input-gradient kernel
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport must be 'nccl' or 'peer'")
+        self.px = None
         n_in, n_out, c_in, c_out = feats.size(0), out.size(0), weights.size(1), weights.size(2)
         p = lambda t: t.data_ptr() if t.numel() > 0 else None
         pairs = imap.numel()
@@ -204,13 +273,18 @@ class BoundSceneLayer:
         self._dgrad_args = (p(grad_out), p(weights), p(in_grad), p(kpos), p(imap), p(omap), pairs, n_in, n_out, c_in, c_out,
                             k_vol, dtype, math)
         self.w_grad, self.part, ws_ptr, ws_bytes, accumulate = w_grad, None, None, 0, 1
+        if self.multi and self.exchange and transport == "peer":
+            self.px = PeerExchange(w_grad.numel(), feats.device, group)
+            self._side = torch.cuda.Stream(device=feats.device)
+            self._ev_sums, self._ev_total = torch.cuda.Event(), torch.cuda.Event()
         if self.fp16 and (self.multi or backend.kernel_family("wgrad", c_in, c_out, feats.dtype, arch80, k_vol) != "tcgen05"):
-            ws = backend.wgrad_workspace(c_in, c_out, k_vol, feats.device)
+            ws = self.px.sums if self.px is not None else backend.wgrad_workspace(c_in, c_out, k_vol, feats.device)
             ws_ptr, ws_bytes = ws.data_ptr(), ws.numel() * 4
             if self.multi:
                 self.part, accumulate = ws[: w_grad.numel()], 0  # fp32 sums, all-reduced, then added to w_grad
         elif not self.fp16 and self.multi:
-            self.part = torch.zeros_like(w_grad)                   # fp32 storage: sums of this rank, all-reduced, then added
+            # fp32 storage: sums of this rank, all-reduced, then added
+            self.part = self.px.sums[: w_grad.numel()].view_as(w_grad) if self.px is not None else torch.zeros_like(w_grad)
         target = self.part if (self.part is not None and not self.fp16) else w_grad
         self._wgrad_args = (p(feats), p(grad_out), p(target), p(kpos), p(imap), p(omap), pairs, n_in, n_out, c_in, c_out,
                             k_vol, dtype, math, ws_ptr, ws_bytes, accumulate)
@@ -233,12 +307,23 @@ class BoundSceneLayer:
             if self.part is not None and not self.fp16:
                 self.part.zero_()
             self._check(self._L.fgms_b200_wgrad(*self._wgrad_args, st))
-            work = dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group, async_op=True) if self.exchange else None
+            work, total = None, self.part
+            if self.px is not None:
+                main = torch.cuda.current_stream(self.device)
+                self._ev_sums.record(main)
+                self._side.wait_event(self._ev_sums)
+                self.px.run(self._side)
+                self._ev_total.record(self._side)
+                total = self.px.reduced[: self.w_grad.numel()]
+            elif self.exchange:
+                work = dist.all_reduce(self.part, op=dist.ReduceOp.SUM, group=self.group, async_op=True)
             self._check(self._L.fgms_b200_dgrad(*self._dgrad_args, st))
             if work is not None:
                 work.wait()
+            if self.px is not None:
+                torch.cuda.current_stream(self.device).wait_event(self._ev_total)
             if self.multi:
                 if self.fp16:
-                    self._check(self._L.fgms_b200_wgrad_finalize(self.w_grad.data_ptr(), self.part.data_ptr(), self.w_grad.numel(), st))
+                    self._check(self._L.fgms_b200_wgrad_finalize(self.w_grad.data_ptr(), total.data_ptr(), self.w_grad.numel(), st))
                 else:
-                    self.w_grad += self.part
+                    self.w_grad += total.view_as(self.w_grad)

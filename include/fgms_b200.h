@@ -185,6 +185,26 @@ int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const in
                             int n_in, int k_vol, int64_t pairs, int32_t* kpos_t, int32_t* in_map_t,
                             int32_t* out_map_t, void* workspace, size_t workspace_bytes, void* stream);
 
+/* ---------------------------------------------------------------------------------------------
+ * Multi-GPU: sum of the ranks' fp32 weight-gradient partial sums over peer memory.  No counterpart in the
+ * reference (it has no multi-GPU path); it stands where a data-parallel caller would otherwise issue an
+ * all-reduce of the [k_vol, c_in, c_out] fp32 sums that fgms_b200_wgrad leaves in its workspace.
+ * One call per rank and step, one process per GPU.  `sums`, `reduced` and `flags` are HOST arrays of `world`
+ * DEVICE pointers, index = rank: entry q is rank q's buffer as mapped into THIS process (peer-mapped memory:
+ * CUDA IPC, cuMemMap or a symmetric-memory allocator; entry `rank` is the local buffer).  sums[q] holds rank
+ * q's `count` partial sums; on completion reduced[rank] (and every other rank's reduced buffer, written by its
+ * owner) holds the totals, added in rank order, the same bits on every rank and run.  flags[q] is
+ * fgms_b200_peer_exchange_flag_bytes(world) bytes, zeroed once before the first call.  `epoch` must be
+ * larger than that of any earlier call on these buffers and equal on all ranks of one call.
+ * The kernel (`ctas` small CTAs; it is meant to run on a side stream beside the input-gradient kernel) waits
+ * for the other ranks with a bound of `wait_limit_cycles` SM cycles (0: about one second); a wait that runs
+ * out is counted in fgms_b200_device_status, the kernel returns, and the totals of that call are undefined.
+ * Only plain loads and stores cross the link. */
+size_t fgms_b200_peer_exchange_flag_bytes(int world);
+int fgms_b200_peer_exchange(const float* const* sums, float* const* reduced, uint32_t* const* flags, int rank,
+                            int world, int64_t count, uint32_t epoch, int64_t wait_limit_cycles, int ctas,
+                            void* stream);
+
 /* Which kernel family the dispatch picks for a shape: 0 = CUDA-core (SIMT), 1 = tcgen05.
  * pass: 0 forward, 1 dgrad, 2 wgrad.  The answer comes from the same plan the launch uses (channel
  * counts multiples of 16 and at most 256, and the operands of this k_vol fitting the current device's

@@ -128,3 +128,18 @@ def test_maps_may_be_null_only_when_empty():
     assert rc == _lib.ERR_INVALID_ARG and "map pointer" in _lib.last_error()
     rc = L.fgms_b200_wgrad_f16_noalloc(one, one, one, one, None, None, 1, 4, 4, 8, 8, 27, 2, None)
     assert rc == _lib.ERR_INVALID_ARG
+
+
+def test_peer_exchange_validates_without_a_device():
+    L = _lib.lib
+    assert L.fgms_b200_peer_exchange_flag_bytes(8) >= (2 * 8 + 1) * 4 and L.fgms_b200_peer_exchange_flag_bytes(8) % 256 == 0
+    assert L.fgms_b200_peer_exchange_flag_bytes(0) == 0 and L.fgms_b200_peer_exchange_flag_bytes(17) == 0
+    tab = (ctypes.c_void_p * 2)(16, 32)  # never dereferenced: validation fails first
+    call = lambda rank, world, count, ctas=8: L.fgms_b200_peer_exchange(tab, tab, tab, rank, world, count, 1, 0, ctas, None)
+    assert call(0, 0, 16) == _lib.ERR_INVALID_ARG
+    assert call(2, 2, 16) == _lib.ERR_INVALID_ARG and "rank" in _lib.last_error()
+    assert call(0, 2, 18) == _lib.ERR_INVALID_ARG and "multiple of 4" in _lib.last_error()
+    assert call(0, 2, 16, ctas=0) == _lib.ERR_INVALID_ARG
+    assert L.fgms_b200_peer_exchange(None, tab, tab, 0, 2, 16, 1, 0, 8, None) == _lib.ERR_INVALID_ARG
+    odd = (ctypes.c_void_p * 2)(16, 40)  # rank 1's buffer is not 16-byte aligned
+    assert L.fgms_b200_peer_exchange(odd, tab, tab, 0, 2, 16, 1, 0, 8, None) == _lib.ERR_INVALID_ARG
