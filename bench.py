@@ -239,7 +239,7 @@ def run_cfg5(args, dev, rank, world, flush):
 
     steps = max(3, min(args.steps, args.cfg5_steps))
     wl, spec, umaps, weights, feats, grad_out = build(1, rank)
-    step = unet.UNetStep(spec, umaps, weights, feats, grad_out)
+    step = unet.UNetStep(spec, umaps, weights, feats, grad_out, transport=args.transport)
     flops_local = unet.step_flops(spec, umaps)
     run = step.run
     graph = None

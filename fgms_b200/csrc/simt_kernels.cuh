@@ -220,7 +220,7 @@ __global__ void __launch_bounds__(SIMT_THREADS) simt_gms_kernel(GmsParams p) {
 // columns of both operands once per chunk and keeps the block's sums in registers until the run ends:
 // one red per value, run and CTA.  Channel counts up to 16 TT on both sides gather every row exactly once.
 // ---------------------------------------------------------------------------------------------
-constexpr int SIMT_WG_TILE = 256;  // pairs per scheduling tile
+constexpr int SIMT_WG_TILE = 64;   // pairs per scheduling tile (small: a small map still spreads over many CTAs)
 constexpr int SIMT_WG_JC = 32;     // pairs per shared-memory chunk
 
 template <typename T, int TT>

@@ -170,17 +170,32 @@ class PeerExchange:
                 self._keep = (buf,)
             self.sums, self.reduced = buf[: self.count], buf[self.count: 2 * self.count]
             ptrs = (base, [b + 4 * self.count for b in base], [b + 8 * self.count for b in base])
-        arr = ctypes.c_void_p * self.world
-        self._tables = tuple(arr(*p) for p in ptrs)
+        self._ptrs = ptrs
+        self._ranges = {}
 
-    def run(self, stream=None):
-        """Enqueue one exchange (every rank of the group must do the same); returns nothing."""
+    def _tables(self, lo: int, hi: int):
+        """Pointer tables of the element range [lo, hi) of every rank's buffers (built once per range)."""
+        import ctypes
+        t = self._ranges.get((lo, hi))
+        if t is None:
+            arr = ctypes.c_void_p * self.world
+            t = (arr(*[b + 4 * lo for b in self._ptrs[0]]), arr(*[b + 4 * lo for b in self._ptrs[1]]), arr(*self._ptrs[2]))
+            self._ranges[(lo, hi)] = t
+        return t
+
+    def run(self, stream=None, lo: int = 0, hi: int | None = None):
+        """Enqueue one exchange of the elements [lo, hi) (default: all).  Every rank of the group must make the
+        same calls in the same order; calls on one object must be enqueued on one stream."""
         import torch
+        hi = self.count if hi is None else hi
+        if lo % 4 or hi % 4 or not 0 <= lo <= hi <= self.count:
+            raise ValueError("range bounds must be multiples of 4 inside the buffer")
         self.epoch += 1
+        sums, reduced, flags = self._tables(lo, hi)
         st = (stream if stream is not None else torch.cuda.current_stream(self.device)).cuda_stream
         with torch.cuda.device(self.device):
-            self._check(self._L.fgms_b200_peer_exchange(self._tables[0], self._tables[1], self._tables[2], self.rank, self.world,
-                                                        self.count, self.epoch, self.wait_limit, self.ctas, st))
+            self._check(self._L.fgms_b200_peer_exchange(sums, reduced, flags, self.rank, self.world, hi - lo, self.epoch,
+                                                        self.wait_limit, self.ctas, st))
 
 
 class SceneParallelLayer:

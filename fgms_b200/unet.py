@@ -162,7 +162,7 @@ class UNetStep:
     """
 
     def __init__(self, spec, umaps: UNetMaps, weights, feats, grad_out, group=None, bucket_bytes: int = 6 << 20,
-                 arch80: bool = True, exchange: bool | None = None):
+                 arch80: bool = True, exchange: bool | None = None, transport: str = "nccl"):
         import torch
         from . import _lib, backend
         from .dist import world_size
@@ -222,7 +222,21 @@ class UNetStep:
         w_total = sum(w_sizes)
         self._w_flat = torch.zeros(w_total, dtype=dt, device=dev)
         self.w_grad = torch.zeros(w_total, dtype=dt, device=dev)
-        self._dw32 = torch.zeros(w_total, dtype=torch.float32, device=dev) if self.multi else None
+        # transport of the buckets' sums between ranks: "nccl" = all-reduce; "peer" = the library's kernel over
+        # peer-mapped memory on a side stream (dist.PeerExchange), whose few small CTAs run beside the backward kernels
+        if transport not in ("nccl", "peer"):
+            raise ValueError("transport must be 'nccl' or 'peer'")
+        self.px = None
+        if self._collective and transport == "peer":
+            from .dist import PeerExchange
+            self.px = PeerExchange(w_total, dev, group)
+            self._dw32, self._total32 = self.px.sums[:w_total], self.px.reduced[:w_total]
+            self._side = torch.cuda.Stream(device=dev)
+            self._ev_bucket = [torch.cuda.Event() for _ in range(64)]
+            self._ev_done = torch.cuda.Event()
+        else:
+            self._dw32 = torch.zeros(w_total, dtype=torch.float32, device=dev) if self.multi else None
+            self._total32 = self._dw32
         self.weights, self.w_grads, self._dw32_views = [None] * len(self.spec), [None] * len(self.spec), [None] * len(self.spec)
         self._w_off = {}
         off = 0
@@ -307,12 +321,14 @@ class UNetStep:
         return self.val[self.out_name]
 
     def backward(self):
+        import torch
         import torch.distributed as dist
         L, check, st = self._L, self._check, self._stream()
+        main = torch.cuda.current_stream(self.device)
         self._grad_flat.zero_()
         self.w_grad.zero_()
         self.grad[self.out_name].copy_(self.grad_out)
-        works = []
+        works, n_bucket = [], 0
         for i in range(len(self.spec) - 1, -1, -1):
             l, wgrad, dgrad = self._bwd[i]
             if l.skip is not None:
@@ -322,13 +338,23 @@ class UNetStep:
             check(L.fgms_b200_wgrad(*wgrad, st))
             if self._collective and i in self._bucket_end:
                 lo, hi = self._bucket_end[i]
-                works.append(dist.all_reduce(self._dw32[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+                if self.px is not None:
+                    ev = self._ev_bucket[n_bucket % len(self._ev_bucket)]
+                    ev.record(main)
+                    self._side.wait_event(ev)
+                    self.px.run(self._side, lo, hi)
+                    n_bucket += 1
+                else:
+                    works.append(dist.all_reduce(self._dw32[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
             if dgrad is not None:
                 check(L.fgms_b200_dgrad(*dgrad, st))
         for w in works:
             w.wait()
+        if self.px is not None:
+            self._ev_done.record(self._side)
+            main.wait_event(self._ev_done)
         if self.multi:
-            check(L.fgms_b200_wgrad_finalize(self.w_grad.data_ptr(), self._dw32.data_ptr(), self.w_grad.numel(), st))
+            check(L.fgms_b200_wgrad_finalize(self.w_grad.data_ptr(), self._total32.data_ptr(), self.w_grad.numel(), st))
 
     def run(self):
         import torch
