@@ -72,6 +72,29 @@ __device__ __forceinline__ bool px_wait_all(const uint32_t* my_flags, int world,
   return timed_out == 0;
 }
 
+// Sum PIECES 16-byte pieces per thread and iteration over up to WMAX ranks (rank order), store the totals to every rank.
+template <int WMAX, int PIECES>
+__device__ __forceinline__ void px_reduce_pieces(const PeerExchangeParams& p, long long first, long long hi, long long stride) {
+  const int world = p.world;
+  for (long long i0 = first; i0 < hi; i0 += stride * PIECES) {
+    float4 v[PIECES][WMAX];
+#pragma unroll
+    for (int u = 0; u < PIECES; ++u)
+#pragma unroll
+      for (int q = 0; q < WMAX; ++q)
+        if (q < world && i0 + u * stride < hi) v[u][q] = px_load4(p.sums[q] + 4 * (i0 + u * stride));
+#pragma unroll
+    for (int u = 0; u < PIECES; ++u) {
+      if (i0 + u * stride >= hi) break;
+      float4 acc = v[u][0];
+#pragma unroll
+      for (int q = 1; q < WMAX; ++q)
+        if (q < world) { acc.x += v[u][q].x; acc.y += v[u][q].y; acc.z += v[u][q].z; acc.w += v[u][q].w; }
+      for (int q = 0; q < world; ++q) px_store4(p.reduced[q] + 4 * (i0 + u * stride), acc);
+    }
+  }
+}
+
 __global__ void __launch_bounds__(PX_THREADS) peer_exchange_kernel(PeerExchangeParams p) {
   const int world = p.world, rank = p.rank;
   uint32_t* mine = p.flags[rank];
@@ -81,20 +104,22 @@ __global__ void __launch_bounds__(PX_THREADS) peer_exchange_kernel(PeerExchangeP
   }
   bool ok = px_wait_all(mine, world, p.epoch, p.wait_limit);
   if (ok) {
+    // A peer load takes microseconds: each thread keeps about eight of them in flight — with few ranks it works on
+    // several 16-byte pieces at once (PX_UNROLL / world of them), with eight or more ranks on one piece at a time.
     const long long n4 = p.count / 4;
     const long long lo = n4 * rank / world, hi = n4 * (rank + 1) / world;
-    for (long long i = lo + (long long)blockIdx.x * PX_THREADS + threadIdx.x; i < hi; i += (long long)gridDim.x * PX_THREADS) {
-      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-      for (int q0 = 0; q0 < world; q0 += 8) {  // eight peer loads in flight, added in rank order
-        float4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (q0 + u < world) v[u] = px_load4(p.sums[q0 + u] + 4 * i);
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (q0 + u < world) { acc.x += v[u].x; acc.y += v[u].y; acc.z += v[u].z; acc.w += v[u].w; }
-      }
-      for (int q = 0; q < world; ++q) px_store4(p.reduced[q] + 4 * i, acc);
+    const long long stride = (long long)gridDim.x * PX_THREADS;
+    const long long first = lo + (long long)blockIdx.x * PX_THREADS + threadIdx.x;
+    if (world == 1) {
+      for (long long i = first; i < hi; i += stride) px_store4(p.reduced[0] + 4 * i, px_load4(p.sums[0] + 4 * i));
+    } else if (world == 2) {
+      px_reduce_pieces<2, 4>(p, first, hi, stride);
+    } else if (world <= 4) {
+      px_reduce_pieces<4, 2>(p, first, hi, stride);
+    } else if (world <= 8) {
+      px_reduce_pieces<8, 1>(p, first, hi, stride);
+    } else {
+      px_reduce_pieces<16, 1>(p, first, hi, stride);
     }
   }
   // the last CTA of this rank to get here tells every rank that this rank's slice is written everywhere

@@ -133,7 +133,7 @@ class PeerExchange:
     no symmetric memory is involved.
     """
 
-    def __init__(self, count: int, device, group=None, ctas: int = 32, wait_limit_cycles: int = 0, buffers=None):
+    def __init__(self, count: int, device, group=None, ctas: int = 0, wait_limit_cycles: int = 0, buffers=None):
         import ctypes
         import torch
         from . import _lib
@@ -141,7 +141,10 @@ class PeerExchange:
         self.device = torch.device(device)
         self.count = (int(count) + 3) // 4 * 4
         self.group = group
-        self.ctas, self.wait_limit, self.epoch = int(ctas), int(wait_limit_cycles), 0
+        # CTAs of 128 threads: enough that a thread sees its slice in a few iterations (a peer load takes
+        # microseconds), few enough to sit beside a persistent kernel: 32 .. 256
+        self.ctas = int(ctas) if ctas else max(32, min(256, self.count // 4 // 128 // 16))
+        self.wait_limit, self.epoch = int(wait_limit_cycles), 0
         if buffers is not None:
             self.rank, self.world, sums, reduced, flags = buffers
             self.sums, self.reduced = sums[self.rank], reduced[self.rank]
@@ -290,7 +293,7 @@ class BoundSceneLayer:
         self.w_grad, self.part, ws_ptr, ws_bytes, accumulate = w_grad, None, None, 0, 1
         if self.multi and self.exchange and transport == "peer":
             self.px = PeerExchange(w_grad.numel(), feats.device, group)
-            self._side = torch.cuda.Stream(device=feats.device)
+            self._side = torch.cuda.Stream(device=feats.device, priority=-1)  # its few CTAs go first when room frees up
             self._ev_sums, self._ev_total = torch.cuda.Event(), torch.cuda.Event()
         if self.fp16 and (self.multi or backend.kernel_family("wgrad", c_in, c_out, feats.dtype, arch80, k_vol) != "tcgen05"):
             ws = self.px.sums if self.px is not None else backend.wgrad_workspace(c_in, c_out, k_vol, feats.device)

@@ -231,7 +231,7 @@ class UNetStep:
             from .dist import PeerExchange
             self.px = PeerExchange(w_total, dev, group)
             self._dw32, self._total32 = self.px.sums[:w_total], self.px.reduced[:w_total]
-            self._side = torch.cuda.Stream(device=dev)
+            self._side = torch.cuda.Stream(device=dev, priority=-1)
             self._ev_bucket = [torch.cuda.Event() for _ in range(64)]
             self._ev_done = torch.cuda.Event()
         else:
