@@ -72,30 +72,32 @@ __device__ __forceinline__ bool px_wait_all(const uint32_t* my_flags, int world,
   return timed_out == 0;
 }
 
-// Sum PIECES 16-byte pieces per thread and iteration over up to WMAX ranks (rank order), store the totals to every rank.
-template <int WMAX, int PIECES>
-__device__ __forceinline__ void px_reduce_pieces(const PeerExchangeParams& p, long long first, long long hi, long long stride) {
+// One 16-byte piece per thread and iteration: the loads of two ranks in flight, added in rank order as they
+// arrive.  Few registers on purpose (see the launch bounds of the kernel).
+__device__ __forceinline__ void px_reduce_slice(const PeerExchangeParams& p, long long first, long long hi, long long stride) {
   const int world = p.world;
-  for (long long i0 = first; i0 < hi; i0 += stride * PIECES) {
-    float4 v[PIECES][WMAX];
-#pragma unroll
-    for (int u = 0; u < PIECES; ++u)
-#pragma unroll
-      for (int q = 0; q < WMAX; ++q)
-        if (q < world && i0 + u * stride < hi) v[u][q] = px_load4(p.sums[q] + 4 * (i0 + u * stride));
-#pragma unroll
-    for (int u = 0; u < PIECES; ++u) {
-      if (i0 + u * stride >= hi) break;
-      float4 acc = v[u][0];
-#pragma unroll
-      for (int q = 1; q < WMAX; ++q)
-        if (q < world) { acc.x += v[u][q].x; acc.y += v[u][q].y; acc.z += v[u][q].z; acc.w += v[u][q].w; }
-      for (int q = 0; q < world; ++q) px_store4(p.reduced[q] + 4 * (i0 + u * stride), acc);
+  for (long long i = first; i < hi; i += stride) {
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    int q = 0;
+    for (; q + 1 < world; q += 2) {
+      const float4 a = px_load4(p.sums[q] + 4 * i);
+      const float4 b = px_load4(p.sums[q + 1] + 4 * i);
+      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+      acc.x += b.x; acc.y += b.y; acc.z += b.z; acc.w += b.w;
     }
+    if (q < world) {
+      const float4 a = px_load4(p.sums[q] + 4 * i);
+      acc.x += a.x; acc.y += a.y; acc.z += a.z; acc.w += a.w;
+    }
+    for (int r = 0; r < world; ++r) px_store4(p.reduced[r] + 4 * i, acc);
   }
 }
 
-__global__ void __launch_bounds__(PX_THREADS) peer_exchange_kernel(PeerExchangeParams p) {
+// At most 32 registers per thread (16 CTAs of 128 threads per SM by the bounds): the kernel is meant to run
+// BESIDE the persistent forward / dgrad kernel, whose 17 warps leave the warp scheduler that holds five of them
+// only 1024 free registers — room for exactly one warp of 32 registers per thread.  With more registers its CTAs
+// are not scheduled until that kernel ends (measured: the exchange then starts when dgrad finishes).
+__global__ void __launch_bounds__(PX_THREADS, 16) peer_exchange_kernel(PeerExchangeParams p) {
   const int world = p.world, rank = p.rank;
   uint32_t* mine = p.flags[rank];
   if (blockIdx.x == 0 && (int)threadIdx.x < world) {
@@ -104,23 +106,9 @@ __global__ void __launch_bounds__(PX_THREADS) peer_exchange_kernel(PeerExchangeP
   }
   bool ok = px_wait_all(mine, world, p.epoch, p.wait_limit);
   if (ok) {
-    // A peer load takes microseconds: each thread keeps about eight of them in flight — with few ranks it works on
-    // several 16-byte pieces at once (PX_UNROLL / world of them), with eight or more ranks on one piece at a time.
     const long long n4 = p.count / 4;
     const long long lo = n4 * rank / world, hi = n4 * (rank + 1) / world;
-    const long long stride = (long long)gridDim.x * PX_THREADS;
-    const long long first = lo + (long long)blockIdx.x * PX_THREADS + threadIdx.x;
-    if (world == 1) {
-      for (long long i = first; i < hi; i += stride) px_store4(p.reduced[0] + 4 * i, px_load4(p.sums[0] + 4 * i));
-    } else if (world == 2) {
-      px_reduce_pieces<2, 4>(p, first, hi, stride);
-    } else if (world <= 4) {
-      px_reduce_pieces<4, 2>(p, first, hi, stride);
-    } else if (world <= 8) {
-      px_reduce_pieces<8, 1>(p, first, hi, stride);
-    } else {
-      px_reduce_pieces<16, 1>(p, first, hi, stride);
-    }
+    px_reduce_slice(p, lo + (long long)blockIdx.x * PX_THREADS + threadIdx.x, hi, (long long)gridDim.x * PX_THREADS);
   }
   // the last CTA of this rank to get here tells every rank that this rank's slice is written everywhere
   __shared__ int last;

@@ -141,9 +141,10 @@ class PeerExchange:
         self.device = torch.device(device)
         self.count = (int(count) + 3) // 4 * 4
         self.group = group
-        # CTAs of 128 threads: enough that a thread sees its slice in a few iterations (a peer load takes
-        # microseconds), few enough to sit beside a persistent kernel: 32 .. 256
-        self.ctas = int(ctas) if ctas else max(32, min(256, self.count // 4 // 128 // 16))
+        # CTAs of 128 threads and 32 registers: one fits on every SM beside a persistent tensor-core kernel.  A peer
+        # load takes microseconds, so a thread should see its part of the slice in very few iterations: one CTA per
+        # 512 values of the buffer, between 32 and 592 (four per SM).
+        self.ctas = int(ctas) if ctas else max(32, min(592, self.count // 512))
         self.wait_limit, self.epoch = int(wait_limit_cycles), 0
         if buffers is not None:
             self.rank, self.world, sums, reduced, flags = buffers
