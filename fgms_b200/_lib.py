@@ -38,6 +38,7 @@ SIGNATURES = {
     "fgms_b200_peer_exchange": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, ctypes.c_uint32, c_int64, c_int, c_void_p]),
     "fgms_b200_kernel_family": (c_int, [c_int] * 6),
     "fgms_b200_fallback_count": (c_int64, []),
+    "fgms_b200_set_reserved_sms": (c_int, [c_int]),
     "fgms_b200_device_status": (c_int64, [c_int]),
     "fgms_b200_launch_count": (c_int64, []),
     "fgms_b200_last_error": (c_char_p, []),

@@ -25,6 +25,8 @@ std::atomic<long long> g_launches{0};
 // launches that the shape alone would have sent to the tensor-core kernels but that ran on the CUDA-core
 // kernels (base pointers not 16-byte aligned): fgms_b200_fallback_count()
 std::atomic<long long> g_fallbacks{0};
+// SMs the persistent kernels leave free (fgms_b200_set_reserved_sms): room for a kernel of another stream
+std::atomic<int> g_reserved_sms{0};
 
 int fail(int code, const char* fmt, ...) {
   va_list ap;
@@ -61,6 +63,8 @@ int device_info(DeviceInfo* out) {
     cached_dev = dev;
   }
   *out = cached;
+  const int keep = g_reserved_sms.load(std::memory_order_relaxed);
+  if (keep > 0) out->sms = cached.sms - keep > 1 ? cached.sms - keep : 1;
   return FGMS_OK;
 }
 
@@ -392,6 +396,12 @@ int fgms_b200_kernel_family(int pass, int c_in, int c_out, int k_vol, int dtype,
 
 int64_t fgms_b200_fallback_count(void) { return g_fallbacks.load(std::memory_order_relaxed); }
 
+int fgms_b200_set_reserved_sms(int n) {
+  if (n < 0 || n > 64) return fail(FGMS_ERR_INVALID_ARG, "reserved SM count %d outside [0, 64]", n);
+  g_reserved_sms.store(n, std::memory_order_relaxed);
+  return FGMS_OK;
+}
+
 // ---------------------------------------------------------------------------------------------
 // Kernel maps (csrc/map_builder.cuh)
 // ---------------------------------------------------------------------------------------------
@@ -544,6 +554,16 @@ int fgms_b200_peer_exchange(const float* const* sums, float* const* reduced, uin
   }
   p.count = count; p.epoch = epoch; p.rank = rank; p.world = world;
   p.wait_limit = wait_limit_cycles > 0 ? wait_limit_cycles : fgms::PX_WAIT_LIMIT_CYCLES;
+  // Same shared-memory carve-out as the tensor-core kernels (the largest): an SM keeps ONE carve-out for all the
+  // CTAs it holds, so a kernel that prefers another one would wait for the persistent kernel's CTAs to leave.
+  static std::atomic<int> carveout_set[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 && !carveout_set[dev].load(std::memory_order_acquire)) {
+    if (cudaFuncSetAttribute(fgms::peer_exchange_kernel, cudaFuncAttributePreferredSharedMemoryCarveout,
+                             cudaSharedmemCarveoutMaxShared) != cudaSuccess)
+      return fail(FGMS_ERR_CUDA, "cudaFuncSetAttribute(carve-out) failed");
+    carveout_set[dev].store(1, std::memory_order_release);
+  }
   fgms::peer_exchange_kernel<<<ctas, fgms::PX_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return check_launch("peer_exchange_kernel");
 }

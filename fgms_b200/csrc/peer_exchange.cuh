@@ -11,7 +11,9 @@
 //   3. reduce     the rank's slice: load it from every rank's `sums` (plain peer loads, fixed order p = 0 .. world-1,
 //                 so the total is the same bits on every run), add, store the total into every rank's `reduced`;
 //   4. announce   the last CTA to finish stores the epoch into flag D[rank] of every rank;
-//   5. wait       until D[p] >= epoch for every p: this rank's `reduced` is complete and no peer still reads its `sums`.
+//   5. wait       that same CTA waits until D[p] >= epoch for every p: this rank's `reduced` is complete and no peer
+//                 still reads its `sums`.  The other CTAs have left by then: a CTA that waited here would hold its
+//                 place on an SM while the CTAs it waits for (its own rank's later ones included) may need one.
 //
 // The reference has no multi-GPU path (backend/spconv.cu has no collective); this replaces the NCCL all-reduce of
 // the data-parallel step where its launch needs SMs the input-gradient kernel holds.  Only plain loads and stores
@@ -120,8 +122,10 @@ __global__ void __launch_bounds__(PX_THREADS, 16) peer_exchange_kernel(PeerExcha
     last = (done % gridDim.x) == 0;  // the counter is never cleared: every call adds gridDim.x
   }
   __syncthreads();
-  if (last && (int)threadIdx.x < world) px_store_flag(p.flags[threadIdx.x] + world + rank, p.epoch);
-  if (ok) ok = px_wait_all(mine + world, world, p.epoch, p.wait_limit);
+  if (last) {
+    if ((int)threadIdx.x < world) px_store_flag(p.flags[threadIdx.x] + world + rank, p.epoch);
+    if (ok) ok = px_wait_all(mine + world, world, p.epoch, p.wait_limit);
+  }
   if (!ok && threadIdx.x == 0) report_problem();
 }
 

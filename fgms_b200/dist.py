@@ -141,10 +141,9 @@ class PeerExchange:
         self.device = torch.device(device)
         self.count = (int(count) + 3) // 4 * 4
         self.group = group
-        # CTAs of 128 threads and 32 registers: one fits on every SM beside a persistent tensor-core kernel.  A peer
-        # load takes microseconds, so a thread should see its part of the slice in very few iterations: one CTA per
-        # 512 values of the buffer, between 32 and 592 (four per SM).
-        self.ctas = int(ctas) if ctas else max(32, min(592, self.count // 512))
+        # CTAs of 128 threads and 32 registers; few enough to be resident all at once beside a persistent kernel
+        # (one per SM at most): one CTA per 2048 values of the buffer, between 16 and 128
+        self.ctas = int(ctas) if ctas else max(16, min(128, self.count // 2048))
         self.wait_limit, self.epoch = int(wait_limit_cycles), 0
         if buffers is not None:
             self.rank, self.world, sums, reduced, flags = buffers

@@ -205,6 +205,14 @@ int fgms_b200_peer_exchange(const float* const* sums, float* const* reduced, uin
                             int world, int64_t count, uint32_t epoch, int64_t wait_limit_cycles, int ctas,
                             void* stream);
 
+/* The tensor-core kernels are persistent: one CTA per SM that holds nearly all of the SM's shared memory and
+ * registers, so a kernel of another stream does not start on that SM before they finish.  A caller that wants
+ * such a kernel to run BESIDE them (fgms_b200_peer_exchange beside the input gradient, a collective) tells the
+ * library to launch on `n` fewer SMs; the setting is process-wide and applies to the launches that follow
+ * (set it around the one call it is meant for).  0 restores the full grid.  No counterpart in the reference,
+ * whose grids follow the problem size (backend/spconv.cu:111-245). */
+int fgms_b200_set_reserved_sms(int n);
+
 /* Which kernel family the dispatch picks for a shape: 0 = CUDA-core (SIMT), 1 = tcgen05.
  * pass: 0 forward, 1 dgrad, 2 wgrad.  The answer comes from the same plan the launch uses (channel
  * counts multiples of 16 and at most 256, and the operands of this k_vol fitting the current device's
