@@ -239,7 +239,8 @@ def run_cfg5(args, dev, rank, world, flush):
 
     steps = max(3, min(args.steps, args.cfg5_steps))
     wl, spec, umaps, weights, feats, grad_out = build(1, rank)
-    step = unet.UNetStep(spec, umaps, weights, feats, grad_out, transport=args.transport)
+    stack_transport = "nccl" if args.transport == "auto" else args.transport
+    step = unet.UNetStep(spec, umaps, weights, feats, grad_out, transport=stack_transport)
     flops_local = unet.step_flops(spec, umaps)
     run = step.run
     graph = None
@@ -297,7 +298,7 @@ def run_cfg5(args, dev, rank, world, flush):
                    "scaling": "weak (one scene per rank)", "voxels_per_level": umaps.voxels,
                    "flops_per_step_all_ranks": flops_all})
     if world > 1:
-        report["allreduce"] = {"buckets": len(step.buckets), "bytes_fp32": int(step.w_grad.numel() * 4),
+        report["allreduce"] = {"transport": stack_transport, "buckets": len(step.buckets), "bytes_fp32": int(step.w_grad.numel() * 4),
                                "exposed_ms_per_step": exposed_ms, "kernels_only_ms_per_step": alone_ms / steps}
         report["multi_gpu_check"] = check
     else:
@@ -506,8 +507,9 @@ def run_ours(args):
     ev = lambda: torch.cuda.Event(enable_timing=True)
     pass_ms = {"fwd": [], "dgrad": [], "wgrad": []}
 
+    layer_transport = "peer" if args.transport == "auto" else args.transport
     bound = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80,
-                            transport=args.transport) if world > 1 else None
+                            transport=layer_transport) if world > 1 else None
     bound_alone = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80,
                                   exchange=False) if world > 1 else None
     ws = backend.wgrad_workspace(wl.c_in, wl.c_out, km.k_vol, dev) if p.dtype == torch.float16 else None
@@ -800,7 +802,7 @@ def run_ours(args):
             line["multi_gpu_check"] = check
             line["exchange"] = {"peer": "fgms_b200_peer_exchange: one kernel per rank over peer-mapped memory (plain loads and stores), on a "
                                         "side stream beside the input-gradient kernel",
-                                "nccl": "NCCL all-reduce of the fp32 sums (async, beside the input-gradient kernel)"}[args.transport]
+                                "nccl": "NCCL all-reduce of the fp32 sums (async, beside the input-gradient kernel)"}[layer_transport]
         if reference_cuda is not None:
             if "step_ms" in reference_cuda:
                 reference_cuda["speedup_of_this_library"] = reference_cuda["step_ms"] / (total_ms / k)
@@ -839,8 +841,9 @@ def main():
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the eager step instead of a CUDA-graph replay of it")
     ap.add_argument("--no-cfg5", dest="cfg5", action="store_false", help="skip the encoder-decoder stack")
     ap.add_argument("--cfg5-steps", type=int, default=20)
-    ap.add_argument("--transport", default="peer", choices=["peer", "nccl"],
-                    help="N > 1: how the weight-gradient sums are exchanged: the library's kernel over peer memory, or an NCCL all-reduce")
+    ap.add_argument("--transport", default="auto", choices=["auto", "peer", "nccl"],
+                    help="N > 1: how the weight-gradient sums are exchanged: the library's kernel over peer memory, an NCCL "
+                         "all-reduce, or (auto) the former for the single layer's 1.8 MB and the latter for the stack's 6 MB+ buckets")
     ap.add_argument("--no-reference-cuda", dest="reference_cuda", action="store_false",
                     help="do not time the reference's CUDA kernels beside this library (they run only when built and sound)")
     args = ap.parse_args()
