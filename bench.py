@@ -549,16 +549,19 @@ def run_ours(args):
     for _ in range(args.warmup):
         prepare(); step(False)
     barrier()
-    # With one rank the launches are captured once into a CUDA graph and replayed, which takes the host out of
-    # the step; the kernels, their order and their arguments are those of the eager step.  --no-graph times the
-    # eager step.  With a collective in the step the launches stay eager.
+    # The launches are captured once into a CUDA graph and replayed, which takes the host out of the step; the
+    # kernels, their order and their arguments are those of the eager step.  --no-graph times the eager step.
+    # With several ranks this holds for the peer-memory exchange (the library's own kernel, which numbers its
+    # calls on the device); a step with an NCCL collective in it stays eager.  Nothing is outstanding on the
+    # process group when the capture starts (barrier + synchronize above), and the capture is thread-local, so
+    # that a CUDA call of another thread of the process cannot invalidate it.
     graph = None
     launches_per_step = None
-    if args.graph and world == 1:
+    if args.graph and (world == 1 or layer_transport == "peer"):
         try:
             c0 = backend.launch_count()
             g = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g):
+            with torch.cuda.graph(g, capture_error_mode="thread_local"):
                 step(False)
             launches_per_step = backend.launch_count() - c0
             graph = g

@@ -19,7 +19,8 @@
 // the data-parallel step where its launch needs SMs the input-gradient kernel holds.  Only plain loads and stores
 // cross the link: no multicast, no atomics on peer memory.  Every wait is bounded; one that runs out is counted
 // (g_device_problems), the kernel returns, and the totals of that call are incomplete.  Epochs only grow, so flags
-// are never cleared.
+// are never cleared.  With epoch = 0 in the parameters the kernel numbers its calls itself (from the rank's CTA
+// counter, which every call raises by the grid size), so that a launch can be replayed from a CUDA graph.
 #pragma once
 
 #include "common.cuh"
@@ -36,7 +37,7 @@ struct PeerExchangeParams {
   uint32_t* flags[PX_MAX_WORLD];     // every rank's flag words: A[0 .. world), D[world .. 2 world), then one CTA counter
   long long count;                   // fp32 values; a multiple of 4
   long long wait_limit;              // cycles a wait may take
-  uint32_t epoch;                    // of this call: larger than that of any call before it
+  uint32_t epoch;                    // of this call: larger than that of any call before it; 0 = numbered on the device
   int rank, world;
 };
 
@@ -102,11 +103,18 @@ __device__ __forceinline__ void px_reduce_slice(const PeerExchangeParams& p, lon
 __global__ void __launch_bounds__(PX_THREADS, 16) peer_exchange_kernel(PeerExchangeParams p) {
   const int world = p.world, rank = p.rank;
   uint32_t* mine = p.flags[rank];
+  // Number of this call.  The CTA counter holds gridDim.x per finished call (the calls before this one have
+  // finished: they were ahead in the stream) plus one per CTA of this call that is done already — fewer than
+  // gridDim.x as long as this CTA is not: counter / gridDim.x is the number of calls before this one.
+  __shared__ uint32_t epoch_s;
+  if (threadIdx.x == 0) epoch_s = p.epoch != 0u ? p.epoch : *reinterpret_cast<volatile uint32_t*>(mine + 2 * world) / gridDim.x + 1u;
+  __syncthreads();
+  const uint32_t epoch = epoch_s;
   if (blockIdx.x == 0 && (int)threadIdx.x < world) {
     __threadfence_system();
-    px_store_flag(p.flags[threadIdx.x] + rank, p.epoch);
+    px_store_flag(p.flags[threadIdx.x] + rank, epoch);
   }
-  bool ok = px_wait_all(mine, world, p.epoch, p.wait_limit);
+  bool ok = px_wait_all(mine, world, epoch, p.wait_limit);
   if (ok) {
     const long long n4 = p.count / 4;
     const long long lo = n4 * rank / world, hi = n4 * (rank + 1) / world;
@@ -123,8 +131,8 @@ __global__ void __launch_bounds__(PX_THREADS, 16) peer_exchange_kernel(PeerExcha
   }
   __syncthreads();
   if (last) {
-    if ((int)threadIdx.x < world) px_store_flag(p.flags[threadIdx.x] + world + rank, p.epoch);
-    if (ok) ok = px_wait_all(mine + world, world, p.epoch, p.wait_limit);
+    if ((int)threadIdx.x < world) px_store_flag(p.flags[threadIdx.x] + world + rank, epoch);
+    if (ok) ok = px_wait_all(mine + world, world, epoch, p.wait_limit);
   }
   if (!ok && threadIdx.x == 0) report_problem();
 }

@@ -35,7 +35,7 @@ constexpr int W3_PROD_THREADS = W3_PROD_WARPS * 32;
 constexpr int W3_THREADS = (W3_PROD_WARP0 + W3_PROD_WARPS) * 32;
 __device__ __forceinline__ int w3_producer_index(int warp) { return warp - W3_PROD_WARP0; }  // < 0: no producer
 constexpr int W3_MAX_STAGES = 12;
-constexpr int W3_MAX_PB = 128;
+constexpr int W3_MAX_PB = 256;
 constexpr int W3_PATCH_BYTES = W3_EPI_WARPS * 4096;
 constexpr int W3_PREFETCH = 4;  // map entries are fetched this many stages ahead
 
@@ -50,7 +50,7 @@ struct W3Shared {
 constexpr int W3_SHARED_BYTES = (sizeof(W3Shared) + 15) & ~15;
 
 struct W3Config {
-  int pb;         // pairs per stage: 32, 64 or 128
+  int pb;         // pairs per stage: 32, 64, 128 or 256
   int n_mtile;    // 1 or 2 accumulator row tiles: all of 128 rows but possibly the last
   int last_m;     // rows of the last tile's MMA: 128, or 64 when at most 64 rows remain
   int pa, pbp;    // 128-byte pieces per staged row of A (enough for every row tile) and of B (n_acc columns)
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
   } else if (w3_producer_index(warp) >= 0) {
     // ------------------------------------------------------------------ producers
     const int pw = w3_producer_index(warp);
-    const int rpw = pb / W3_PROD_WARPS;  // rows of a stage owned by this warp: 4, 8 or 16
+    const int rpw = pb / W3_PROD_WARPS;  // rows of a stage owned by this warp: 4, 8, 16 or 32
     const int n_pass = rpw >> 2;         // a warp-wide copy covers 4 rows x 128 bytes
     const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
     const uint8_t* og = static_cast<const uint8_t*>(p.out_grad);
@@ -143,48 +143,49 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     // rs, rs + 4, ... of the warp's block: one shuffle and one address per row, then one cp.async per
     // piece at a fixed distance (128 bytes in global memory, `lbo` in shared memory).
     const int rs = lane >> 3, cc = lane & 7;
-    uint32_t dst_rel[4];  // piece 0 of row rs + 4 u, relative to the operand's start in the stage
+    // piece 0 of row rs + 4 u, relative to the operand's start in the stage: rows 8 apart are 1024 bytes apart in
+    // both layouts, so two offsets (u even / odd) and a multiple of 1024 give all of them
+    uint32_t dst_rel[2];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 2; ++u) {
       const uint32_t row = (uint32_t)(pw * rpw + rs + 4 * u);
       dst_rel[u] = TF32 ? mnmajor32_offset(row, (uint32_t)cc * 16u, lbo, 512u) : mnmajor_offset(row, (uint32_t)cc * 16u, lbo, 1024u);
     }
     const uint8_t* feats_c = feats + cc * 16;
     const uint8_t* og_c = og + cc * 16;
-    // lanes 0..15 fetch in_map of the warp's rows, lanes 16..31 out_map (-1 beyond the stage)
-    auto load_entry = [&](const G3Walk& w) -> int {
+    // lane r < rpw fetches both map entries of the warp's row r (-1 beyond the stage)
+    auto load_entry = [&](const G3Walk& w, int* ea, int* eb) {
       int base, cnt;
       w3_stage(w, pb, kpos_s, &base, &cnt);
-      const int r = lane & 15;
-      const int row = pw * rpw + r;
-      if (r >= rpw || row >= cnt) return -1;
-      return __ldg((lane < 16 ? p.in_map : p.out_map) + base + row);
+      const int row = pw * rpw + lane;
+      *ea = *eb = -1;
+      if (lane < rpw && row < cnt) {
+        *ea = __ldg(p.in_map + base + row);
+        *eb = __ldg(p.out_map + base + row);
+      }
     };
     G3Walk pf;
     pf.init(tile_start, n_seg, t0);
-    int e[W3_PREFETCH];
+    int ea[W3_PREFETCH], eb[W3_PREFETCH];
 #pragma unroll
     for (int d = 0; d < W3_PREFETCH; ++d) {
-      e[d] = (pf.t < t1) ? load_entry(pf) : -1;
+      ea[d] = eb[d] = -1;
+      if (pf.t < t1) load_entry(pf, &ea[d], &eb[d]);
       pf.next(tile_start, n_seg);
     }
     int s = 0, sg = 0;  // stage, and its position in its group
     uint32_t ph = 0;
     for (int t = t0; t < t1 && ok; ++t) {
-      int cur = e[0];
+      int cur_a = ea[0], cur_b = eb[0];
 #pragma unroll
-      for (int d = 0; d + 1 < W3_PREFETCH; ++d) e[d] = e[d + 1];
-      e[W3_PREFETCH - 1] = (pf.t < t1) ? load_entry(pf) : -1;
+      for (int d = 0; d + 1 < W3_PREFETCH; ++d) { ea[d] = ea[d + 1]; eb[d] = eb[d + 1]; }
+      ea[W3_PREFETCH - 1] = eb[W3_PREFETCH - 1] = -1;
+      if (pf.t < t1) load_entry(pf, &ea[W3_PREFETCH - 1], &eb[W3_PREFETCH - 1]);
       pf.next(tile_start, n_seg);
       // a pair is used only if both its entries are inside the tensors
-      {
-        const int other = __shfl_xor_sync(0xffffffffu, cur, 16);
-        const int a = lane < 16 ? cur : other, b = lane < 16 ? other : cur;
-        const bool okp = (unsigned)a < (unsigned)p.n_in && (unsigned)b < (unsigned)p.n_out;
-        if (!okp) {
-          if (lane < 16 && (a != -1 || b != -1)) report_problem();  // counted once per skipped pair
-          cur = -1;
-        }
+      if (!((unsigned)cur_a < (unsigned)p.n_in && (unsigned)cur_b < (unsigned)p.n_out)) {
+        if (cur_a != -1 || cur_b != -1) report_problem();  // counted once per skipped pair
+        cur_a = cur_b = -1;
       }
       if (sg == 0) {
         ok = g3_wait(&sh->empty[s], ph ^ 1u, abort_flag);
@@ -193,14 +194,15 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
       const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
       const uint32_t sb = sa + a_bytes;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         if (u < n_pass) {
-          const int ia = __shfl_sync(0xffffffffu, cur, rs + 4 * u);
-          const int ib = __shfl_sync(0xffffffffu, cur, 16 + rs + 4 * u);
+          const int ia = __shfl_sync(0xffffffffu, cur_a, rs + 4 * u);
+          const int ib = __shfl_sync(0xffffffffu, cur_b, rs + 4 * u);
           const uint32_t na = ia >= 0 ? 16u : 0u, nb = ib >= 0 ? 16u : 0u;  // 0 bytes read: the chunk is zero-filled
           const uint8_t* pa = feats_c + (size_t)max(ia, 0) * a_row_bytes;
           const uint8_t* pb_ = og_c + (size_t)max(ib, 0) * b_row_bytes;
-          const uint32_t da = sa + dst_rel[u], db = sb + dst_rel[u];
+          const uint32_t rel = dst_rel[u & 1] + (uint32_t)(u >> 1) * 1024u;
+          const uint32_t da = sa + rel, db = sb + rel;
 #pragma unroll
           for (int h = 0; h < 8; ++h)
             if (h < nha) cp_async16_n(da + (uint32_t)h * lbo, pa + h * 128, na);

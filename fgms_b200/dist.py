@@ -144,7 +144,7 @@ class PeerExchange:
         # CTAs of 128 threads and 32 registers; few enough to be resident all at once beside a persistent kernel
         # (one per SM at most): one CTA per 2048 values of the buffer, between 16 and 128
         self.ctas = int(ctas) if ctas else max(16, min(128, self.count // 2048))
-        self.wait_limit, self.epoch = int(wait_limit_cycles), 0
+        self.wait_limit = int(wait_limit_cycles)
         if buffers is not None:
             self.rank, self.world, sums, reduced, flags = buffers
             self.sums, self.reduced = sums[self.rank], reduced[self.rank]
@@ -193,11 +193,11 @@ class PeerExchange:
         hi = self.count if hi is None else hi
         if lo % 4 or hi % 4 or not 0 <= lo <= hi <= self.count:
             raise ValueError("range bounds must be multiples of 4 inside the buffer")
-        self.epoch += 1
         sums, reduced, flags = self._tables(lo, hi)
         st = (stream if stream is not None else torch.cuda.current_stream(self.device)).cuda_stream
         with torch.cuda.device(self.device):
-            self._check(self._L.fgms_b200_peer_exchange(sums, reduced, flags, self.rank, self.world, hi - lo, self.epoch,
+            # epoch 0: the kernel numbers its calls on the device, so the launch may be replayed from a CUDA graph
+            self._check(self._L.fgms_b200_peer_exchange(sums, reduced, flags, self.rank, self.world, hi - lo, 0,
                                                         self.wait_limit, self.ctas, st))
 
 

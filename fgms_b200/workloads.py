@@ -11,6 +11,8 @@ recorded with every result.
 ``cfg3b``         the transposed 2x2x2 convolution back to the fine voxels, tf32 64→32
 ``cfg4``          two overlaid 64-beam LiDAR sweeps voxelised at 5 cm (~145 k voxels),
                   3x3x3 submanifold, fp16 128→128
+``cfg5l0``        the finest-resolution layer of the cfg5 stack on its own: ~120 k-voxel surface
+                  cloud, 3x3x3 submanifold, fp16 32→32 (small channels: gather-bound)
 ================  =====================================================================
 
 ``cfg5`` is not one layer but a stack (``unet_workload``): the MinkUNet-style encoder-decoder of
@@ -26,7 +28,7 @@ from . import clouds, maps
 __all__ = ["Workload", "LayerTensors", "get", "NAMES", "flops", "algorithmic_bytes", "UNetWorkload", "unet_workload",
            "layer_bytes"]
 
-NAMES = ("cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4")
+NAMES = ("cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4", "cfg5l0")
 
 
 @dataclass(frozen=True)
@@ -65,6 +67,11 @@ def get(name: str, seed_offset: int = 0) -> Workload:
     if name == "cfg4":
         km = maps.build_submanifold_map(clouds.lidar_cloud(104 + s, sweeps=2))
         return Workload(name, "64-beam LiDAR, 2 sweeps, 5 cm voxels (~145k), subm 3x3x3, fp16 128->128", km, 128, 128, "fp16", 104 + s)
+    if name == "cfg5l0":
+        # one layer of the cfg5 stack on its own: the finest-resolution 32 -> 32 submanifold convolution (the small-channel,
+        # gather-bound shape that dominates the stack's step), on the first scene of the stack's batch
+        km = maps.build_submanifold_map(clouds.surface_cloud(120_000, 256, 105 + 17 * (s // 1000)))
+        return Workload(name, "cfg5 finest level: surface ~120k voxels in 256^3, subm 3x3x3, fp16 32->32", km, 32, 32, "fp16", 105 + s)
     raise KeyError(name)
 
 

@@ -195,7 +195,9 @@ int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const in
  * q's `count` partial sums; on completion reduced[rank] (and every other rank's reduced buffer, written by its
  * owner) holds the totals, added in rank order, the same bits on every rank and run.  flags[q] is
  * fgms_b200_peer_exchange_flag_bytes(world) bytes, zeroed once before the first call.  `epoch` must be
- * larger than that of any earlier call on these buffers and equal on all ranks of one call.
+ * larger than that of any earlier call on these buffers and equal on all ranks of one call; with epoch = 0
+ * the kernel numbers the calls itself (first call 1, then 2, ...: every rank must then make the same calls with
+ * the same `ctas` on these buffers), which lets a launch be replayed from a CUDA graph.
  * The kernel (`ctas` small CTAs; it is meant to run on a side stream beside the input-gradient kernel) waits
  * for the other ranks with a bound of `wait_limit_cycles` SM cycles (0: about one second); a wait that runs
  * out is counted in fgms_b200_device_status, the kernel returns, and the totals of that call are undefined.
