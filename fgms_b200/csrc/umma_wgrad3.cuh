@@ -53,6 +53,9 @@ struct W3Config {
   int pb;         // pairs per stage: 32, 64, 128 or 256
   int n_mtile;    // 1 or 2 accumulator row tiles: all of 128 rows but possibly the last
   int last_m;     // rows of the last tile's MMA: 128, or 64 when at most 64 rows remain
+  int alias;      // 1: the last tile's second piece is its first one read again (descriptor LBO = 0) instead of a
+                  //    piece of its own — tf32 with at most 32 rows left: an M = 64 MMA reads two 32-row pieces, only
+                  //    one is real, and the rows it repeats land in accumulator rows that are never written out
   int pa, pbp;    // 128-byte pieces per staged row of A (enough for every row tile) and of B (n_acc columns)
   int n_acc;      // TMEM columns of one row tile: c_out rounded up to a whole piece
   int smem;       // dynamic shared memory of the launch
@@ -222,6 +225,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     const uint32_t idesc_last = make_idesc(TF32, true, true, cfg.last_m, cfg.n_acc);
     const uint32_t sbo = TF32 ? 512u : 1024u, ltype = TF32 ? 1u : 2u;
     const uint32_t mtile_stride = (uint32_t)ES * lbo;  // a 128-row tile spans 128 * ES / 128 pieces
+    const uint32_t last_lbo = cfg.alias ? 0u : lbo;
     G3Walk cur;
     cur.init(tile_start, n_seg, t0);
     int s = 0, sg = 0, run_i = 0, cur_seg = -1;
@@ -253,7 +257,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
           const uint32_t kadv = (uint32_t)ks * UK * 128u;
           const uint64_t b_desc = make_sdesc(sb + kadv, lbo, sbo, ltype);
           for (int mt = 0; mt < cfg.n_mtile; ++mt) {
-            const uint64_t a_desc = make_sdesc(sa + kadv + mt * mtile_stride, lbo, sbo, ltype);
+            const uint64_t a_desc = make_sdesc(sa + kadv + mt * mtile_stride, mt + 1 == cfg.n_mtile ? last_lbo : lbo, sbo, ltype);
             mma_ss<TF32>(tmem_base + (uint32_t)buf * buf_cols + (uint32_t)(mt * cfg.n_acc), a_desc, b_desc,
                          mt + 1 == cfg.n_mtile ? idesc_last : idesc_full, !(first && ks == 0));
           }
@@ -369,8 +373,10 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   if (!umma_supported(c_in, c_out, es)) return false;
   const int epr = 128 / es;  // elements per 128-byte piece
   cfg->n_mtile = (c_in + 127) / 128;
-  cfg->last_m = (c_in - 128 * (cfg->n_mtile - 1)) <= 64 ? 64 : 128;
-  cfg->pa = (cfg->n_mtile - 1) * es + (cfg->last_m == 128 ? es : es / 2);  // a 128-row tile reads 128 / epr = es pieces
+  const int rem = c_in - 128 * (cfg->n_mtile - 1);
+  cfg->last_m = rem <= 64 ? 64 : 128;
+  cfg->alias = (es == 4 && rem <= 32) ? 1 : 0;
+  cfg->pa = (cfg->n_mtile - 1) * es + (cfg->last_m == 128 ? es : es / 2) - cfg->alias;  // a 128-row tile reads 128 / epr = es pieces
   cfg->n_acc = (c_out + epr - 1) / epr * epr;
   cfg->pbp = cfg->n_acc / epr;
   const int buf_cols = cfg->n_mtile * cfg->n_acc;
