@@ -508,8 +508,23 @@ def run_ours(args):
     pass_ms = {"fwd": [], "dgrad": [], "wgrad": []}
 
     layer_transport = "peer" if args.transport == "auto" else args.transport
-    bound = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80,
-                            transport=layer_transport) if world > 1 else None
+    bound = None
+    if world > 1:
+        make = lambda tr: BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap,
+                                          p.arch80, transport=tr)
+        if layer_transport == "peer":
+            # peer-mapped buffers need the symmetric-memory allocator and peer access between the GPUs; where a rank
+            # cannot get them, all ranks agree to use NCCL instead
+            try:
+                bound = make("peer")
+            except Exception as exc:
+                sys.stderr.write(f"bench: rank {rank}: peer-mapped buffers unavailable ({exc!r})\n")
+            agreed = torch.tensor([1.0 if bound is not None else 0.0], device=dev)
+            dist.all_reduce(agreed, op=dist.ReduceOp.MIN)
+            if agreed.item() < 1:
+                layer_transport, bound = "nccl", None
+        if bound is None:
+            bound = make(layer_transport)
     bound_alone = BoundSceneLayer(p.feats, p.weights, p.grad_out, out, in_grad, w_grad, p.kpos, p.imap, p.omap, p.arch80,
                                   exchange=False) if world > 1 else None
     ws = backend.wgrad_workspace(wl.c_in, wl.c_out, km.k_vol, dev) if p.dtype == torch.float16 else None
@@ -654,6 +669,29 @@ def run_ours(args):
         dist.all_reduce(flag, op=dist.ReduceOp.MIN)
         check["ok"] = bool(flag.item() > 0)
         check["what"] = "all-reduced w_grad vs the sum of every rank's own fp32 sums (all_gather); out / in_grad vs the single-rank entry points"
+
+    # ---- where the peer exchange sits in the step (eager steps, events on both streams) -----------------------
+    timeline = None
+    if world > 1 and bound.px is not None:
+        rows = []
+        inner = bound.px.run
+        for it in range(15):
+            prepare()
+            t0, t1, x0, x1 = ev(), ev(), ev(), ev()
+
+            def timed_run(stream=None, *a, _x0=x0, _x1=x1):
+                _x0.record(stream); inner(stream, *a); _x1.record(stream)
+
+            bound.px.run = timed_run
+            t0.record(); bound.forward(); bound.backward(); t1.record()
+            bound.px.run = inner
+            barrier()
+            if it >= 5:
+                rows.append((t0.elapsed_time(x0), t0.elapsed_time(x1), t0.elapsed_time(t1)))
+        m = [statistics.mean(c) * 1e3 for c in zip(*rows)]
+        timeline = {"what": "eager step of this rank, microseconds after the step's first kernel starts; the exchange is enqueued on "
+                            "its side stream when the weight-gradient kernel has finished, the input-gradient kernel runs beside it",
+                    "exchange_starts_us": m[0], "exchange_ends_us": m[1], "step_ends_us": m[2]}
 
     # ---- end to end with host buffers ----------------------------------------------------------
     # Three streams and two sets of device / host buffers: the upload of step i + 1 and the download of
@@ -803,6 +841,8 @@ def run_ours(args):
             line["pass_ms"]["step_kernels_only"] = alone_ms
             line["pass_ms"]["allreduce_exposed"] = total_ms / k - alone_ms
             line["multi_gpu_check"] = check
+            if timeline is not None:
+                line["exchange_timeline"] = timeline
             line["exchange"] = {"peer": "fgms_b200_peer_exchange: one kernel per rank over peer-mapped memory (plain loads and stores), on a "
                                         "side stream beside the input-gradient kernel",
                                 "nccl": "NCCL all-reduce of the fp32 sums (async, beside the input-gradient kernel)"}[layer_transport]

@@ -143,3 +143,11 @@ def test_peer_exchange_validates_without_a_device():
     assert L.fgms_b200_peer_exchange(None, tab, tab, 0, 2, 16, 1, 0, 8, None) == _lib.ERR_INVALID_ARG
     odd = (ctypes.c_void_p * 2)(16, 40)  # rank 1's buffer is not 16-byte aligned
     assert L.fgms_b200_peer_exchange(odd, tab, tab, 0, 2, 16, 1, 0, 8, None) == _lib.ERR_INVALID_ARG
+
+
+def test_reserved_sm_setting_validates():
+    L = _lib.lib
+    assert L.fgms_b200_set_reserved_sms(-1) == _lib.ERR_INVALID_ARG
+    assert L.fgms_b200_set_reserved_sms(65) == _lib.ERR_INVALID_ARG
+    assert L.fgms_b200_set_reserved_sms(8) == _lib.OK
+    assert L.fgms_b200_set_reserved_sms(0) == _lib.OK

@@ -243,3 +243,15 @@ def test_unaligned_tensors_fall_back_and_are_counted():
     out = p.run_fwd()
     assert backend.fallback_count() == before + 1
     assert err(out, p.ref_fwd()) <= TOL["fp16"]
+
+
+def test_results_do_not_depend_on_the_number_of_sms_used():
+    """The persistent kernels on fewer SMs (room left for a kernel of another stream) compute the same layer."""
+    from fgms_b200 import _lib
+    p = Problem(_sub_map(3000, 18, 8), 128, 64, seed=2, mode="fp16")
+    try:
+        assert _lib.lib.fgms_b200_set_reserved_sms(16) == 0
+        _check_all(p)
+    finally:
+        _lib.lib.fgms_b200_set_reserved_sms(0)
+    _check_all(p)
