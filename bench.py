@@ -27,8 +27,8 @@ configuration the 60 %-of-roofline target is stated on).  The metric is effectiv
 With N > 1 (torchrun, one rank per GPU) every rank holds its own scene of the same kind (weak
 scaling, data parallel); the weight-gradient partial sums are combined with one NCCL all-reduce
 inside the timed step, and the exchanged result is checked on the GPUs after the timed loop
-(``multi_gpu_check``).  ``--shard rows`` instead cuts ONE scene over the ranks by output-row range
-(forward) / input-row range (dgrad) and reports that step as ``strong_scaling``.
+(``multi_gpu_check``).  Beside it ONE scene is cut over the ranks by output-row range (forward) /
+input-row range (dgrad) and that step is reported as ``strong_scaling`` (``--shard scenes`` skips it).
 Rank 0 prints ONE JSON line.
 """
 from __future__ import annotations
@@ -165,8 +165,6 @@ def workload_config(wl, gpus, shard):
     km = wl.kmap
     if gpus == 1:
         par = "single GPU"
-    elif shard == "rows":
-        par = f"one scene cut over {gpus} GPUs by output / input row range, wgrad all-reduce"
     else:
         par = f"dp{gpus} (one scene per GPU, wgrad all-reduce)"
     return {"workload": f"{wl.name}: {wl.description}", "n_in": km.n_in, "n_out": km.n_out, "pairs": km.pairs,
@@ -489,8 +487,8 @@ def run_ours(args):
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=dev)
 
-    shard_rows = args.shard == "rows" and world > 1
-    wl = workloads.get(args.workload, seed_offset=0 if shard_rows else 1000 * rank)
+    shard_rows = args.shard != "scenes" and world > 1
+    wl = workloads.get(args.workload, seed_offset=1000 * rank)
     km = wl.kmap
     p = workloads.LayerTensors(km, wl.c_in, wl.c_out, wl.seed, wl.mode, device=dev)
     layer = SceneParallelLayer(p.kpos, p.imap, p.omap, p.qsum, p.arch80)
@@ -778,7 +776,13 @@ def run_ours(args):
         reference_cuda = run_reference_cuda(wl, p, prepare, ev)
 
     fallbacks = backend.fallback_count() - fallbacks0
-    strong = run_row_shard(args, dev, rank, world, wl, p, flush) if shard_rows else None
+    strong = None
+    if shard_rows:
+        # every rank holds the SAME scene here (rank 0's) and works on its own row ranges of it
+        wl0 = workloads.get(args.workload, seed_offset=0)
+        p0 = p if rank == 0 else workloads.LayerTensors(wl0.kmap, wl0.c_in, wl0.c_out, wl0.seed, wl0.mode, device=dev)
+        strong = run_row_shard(args, dev, rank, world, wl0, p0, flush)
+        del p0
     cfg5, cfg5_check = (None, None)
     if args.cfg5:
         del d_in, d_out
@@ -878,8 +882,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--workload", default="cfg4")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--shard", default="scenes", choices=["scenes", "rows"],
-                    help="N > 1: 'scenes' = one scene per rank (weak scaling); 'rows' also cuts one scene by row range and reports strong_scaling")
+    ap.add_argument("--shard", default="both", choices=["both", "scenes"],
+                    help="N > 1: the headline is always one scene per rank (weak scaling); 'both' also cuts ONE scene over the "
+                         "ranks by row range and reports that step as strong_scaling, 'scenes' skips it")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", dest="graph", action="store_false", help="time the eager step instead of a CUDA-graph replay of it")
     ap.add_argument("--no-cfg5", dest="cfg5", action="store_false", help="skip the encoder-decoder stack")

@@ -30,7 +30,7 @@ from dataclasses import dataclass
 import numpy as np
 
 __all__ = ["LayerSpec", "minkunet_spec", "UNetMaps", "build_unet_maps", "build_unet_maps_host", "unet_weights",
-           "UNetStep", "layer_flops", "step_flops"]
+           "UNetStep", "layer_flops", "step_flops", "flat_layout", "plan_buckets"]
 
 
 @dataclass(frozen=True)
@@ -148,6 +148,35 @@ def step_flops(spec, umaps: UNetMaps) -> float:
     return sum(layer_flops(l, int(umaps.of(l).pairs), i == 0) for i, l in enumerate(spec))
 
 
+def flat_layout(spec, align: int = 128):
+    """Where every layer's ``[k_vol, c_in, c_out]`` block sits in the flat weight / weight-gradient buffers: layers in
+    BACKWARD order (the order their gradients become ready), every block padded to a multiple of ``align`` elements.
+    Returns ``({layer index: (first element, one past the padded block)}, total elements)``."""
+    off, where = 0, {}
+    for i in range(len(spec) - 1, -1, -1):
+        n = spec[i].k_vol * spec[i].c_in * spec[i].c_out
+        size = (n + align - 1) // align * align
+        where[i] = (off, off + size)
+        off += size
+    return where, off
+
+
+def plan_buckets(spec, where, bucket_bytes: int):
+    """Cut the flat buffer into buckets of consecutive layers (backward order), each closed once it holds at least
+    ``bucket_bytes`` of fp32 sums (the last one takes what is left).  Returns ``[(first element, one past the last,
+    index of the layer whose weight gradient completes the bucket)]``: that layer's gradient is the last of the bucket to
+    be enqueued, so the bucket's exchange can start right after it."""
+    buckets, start, acc = [], 0, 0
+    order = list(range(len(spec) - 1, -1, -1))
+    for i in order:
+        lo, hi = where[i]
+        acc += (hi - lo) * 4
+        if acc >= bucket_bytes or i == order[-1]:
+            buckets.append((start, hi, i))
+            start, acc = hi, 0
+    return buckets
+
+
 class UNetStep:
     """Forward + backward of the stack over fixed device buffers, as straight C-ABI calls.
 
@@ -218,8 +247,8 @@ class UNetStep:
 
         # ---- weights and weight gradients, flat, in BACKWARD order (the order the gradients become ready) -----
         order = list(range(len(self.spec)))[::-1]
-        w_sizes = [pad(self.spec[i].k_vol * self.spec[i].c_in * self.spec[i].c_out) for i in order]
-        w_total = sum(w_sizes)
+        where, w_total = flat_layout(self.spec)
+        w_sizes = [where[i][1] - where[i][0] for i in order]
         self._w_flat = torch.zeros(w_total, dtype=dt, device=dev)
         self.w_grad = torch.zeros(w_total, dtype=dt, device=dev)
         # transport of the buckets' sums between ranks: "nccl" = all-reduce; "peer" = the library's kernel over
@@ -253,15 +282,7 @@ class UNetStep:
             self._w_off[i] = (off, off + sz)
             off += sz
         # buckets: consecutive layers in backward order, closed when they reach `bucket_bytes` of fp32 sums
-        self.buckets = []  # (first element, one past the last, index of the layer whose wgrad completes it)
-        if self.multi:
-            start, acc = 0, 0
-            for i in order:
-                lo, hi = self._w_off[i]
-                acc += (hi - lo) * 4
-                if acc >= bucket_bytes or i == order[-1]:
-                    self.buckets.append((start, hi, i))
-                    start, acc = hi, 0
+        self.buckets = plan_buckets(self.spec, where, bucket_bytes) if self.multi else []
 
         # a small fp32 workspace for layers whose weight gradient has no single-launch fp16 form (single rank only)
         self._ws = None

@@ -122,3 +122,59 @@ def test_tensor_side_cut_equals_the_numpy_cut(world, by):
         assert cut.row_range == (int(bounds[r]), int(bounds[r + 1]))
         assert np.array_equal(cut.kpos.numpy(), s.kpos)
         assert np.array_equal(cut.imap.numpy(), s.imap) and np.array_equal(cut.omap.numpy(), s.omap)
+
+
+def _unet_rank(rank, world, port, out_dir):
+    """One CPU rank of the data-parallel stack: its own scene, the oracle as the per-layer compute, the weight-gradient
+    sums of all layers in one flat buffer exchanged bucket by bucket as the buckets complete in the backward."""
+    from fgms_b200 import unet
+    from oracle import unet_oracle
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    spec = unet.minkunet_spec(4, (16, 16, 32))
+    coords = clouds.surface_cloud(500, 32, 40 + rank)
+    um = unet.build_unet_maps_host(coords, levels=2)
+    w = unet.unet_weights(spec, unet.build_unet_maps_host(clouds.surface_cloud(500, 32, 40), levels=2), 3, dtype=np.float64)  # same on all ranks
+    rng = np.random.default_rng(rank)
+    f, g = rng.standard_normal((um.voxels[0], 4)), rng.standard_normal((um.voxels[0], 16))
+    val = unet_oracle.forward(spec, um, w, f)
+    _, w_grads = unet_oracle.backward(spec, um, w, val, g)
+    where, total = unet.flat_layout(spec)
+    buckets = unet.plan_buckets(spec, where, bucket_bytes=40_000)
+    flat = torch.zeros(total, dtype=torch.float64)
+    ends = {last: (lo, hi) for lo, hi, last in buckets}
+    works = []
+    for i in range(len(spec) - 1, -1, -1):            # backward order: layer i's gradient becomes ready
+        lo, _ = where[i]
+        flat[lo: lo + w_grads[i].size] = torch.from_numpy(w_grads[i].ravel())
+        if i in ends:
+            a, b = ends[i]
+            works.append(dist.all_reduce(flat[a:b], async_op=True))
+    for wk in works:
+        wk.wait()
+    np.save(os.path.join(out_dir, f"own{rank}.npy"), np.concatenate([x.ravel() for x in w_grads]))
+    np.save(os.path.join(out_dir, f"flat{rank}.npy"), flat.numpy())
+    dist.destroy_process_group()
+
+
+def test_bucketed_exchange_of_a_stack_on_cpu_ranks(tmp_path):
+    from fgms_b200 import unet
+    world = 2
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_unet_rank, args=(world, port, str(tmp_path)), nprocs=world, join=True)
+    spec = unet.minkunet_spec(4, (16, 16, 32))
+    where, total = unet.flat_layout(spec)
+    buckets = unet.plan_buckets(spec, where, bucket_bytes=40_000)
+    assert len(buckets) >= 2 and buckets[0][0] == 0 and buckets[-1][1] == total
+    assert all(a[1] == b[0] for a, b in zip(buckets, buckets[1:]))
+    own = [np.load(tmp_path / f"own{r}.npy") for r in range(world)]
+    flats = [np.load(tmp_path / f"flat{r}.npy") for r in range(world)]
+    assert np.array_equal(flats[0], flats[1])
+    pos = 0
+    for i, l in enumerate(spec):                        # `own` is in layer order, the flat buffer in backward order
+        n = l.k_vol * l.c_in * l.c_out
+        lo = where[i][0]
+        assert np.allclose(flats[0][lo: lo + n], own[0][pos: pos + n] + own[1][pos: pos + n], rtol=1e-12, atol=1e-12), l.name
+        pos += n
