@@ -304,6 +304,15 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
   } else if (warp == G3_MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
     const uint32_t idesc = make_idesc(TF32, false, !TRANS_W, G3_TILE_M, cfg.n_mma);
+    // Descriptors of stage 0 / weight buffer 0 at K step 0; every other one differs from them only in the start
+    // address field (bits 0-13, address >> 4, which never carries: shared memory ends below 2^18), so the issue
+    // loop adds small integers instead of rebuilding descriptors — the loop runs on one lane and its length is
+    // what the tile rate sees.
+    const uint64_t a_desc0 = make_sdesc(smem_u32(sStage), 16u, 1024u);
+    const uint64_t b_desc0 = TRANS_W ? make_sdesc(smem_u32(sW), 16u, 1024u)
+                                     : make_sdesc(smem_u32(sW), (uint32_t)p.k_dim * 128u, TF32 ? 512u : 1024u, TF32 ? 1u : 2u);
+    const uint32_t b_kc_step = TRANS_W ? (uint32_t)p.n_dim * 8u : (uint32_t)EPR * 8u;  // one 128-byte K chunk further, in 16-byte units
+    const uint32_t b_ks_step = TRANS_W ? 2u : (32u / ES) * 8u;                          // one 32-byte MMA step further
     G3Walk cur;
     cur.init(tile_start, n_seg, t0);
     int s = 0;
@@ -324,28 +333,22 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)(buf * cfg.n_acc);
-      const uint32_t sw = smem_u32(sW + (size_t)wb * cfg.w_bytes);
+      const uint64_t b_desc_w = b_desc0 + (uint64_t)((uint32_t)wb * ((uint32_t)cfg.w_bytes >> 4));
       for (int kc = 0; kc < kch && ok; ++kc) {
         ok = g3_wait(&sh->full[s], ph, abort_flag);
         if (!ok) break;
         if (lane == 0) {
           fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
           tc_fence_after();
-          const uint32_t sa = smem_u32(sStage + (size_t)s * G3_STAGE_BYTES);
+          const uint64_t a_desc_s = a_desc0 + (uint64_t)((uint32_t)s * (G3_STAGE_BYTES >> 4));
+          const uint64_t b_desc_kc = b_desc_w + (uint64_t)((uint32_t)kc * b_kc_step);
           const int n_ks = FULL ? 4 : min(4, (k_bytes - kc * 128) >> 5);  // 32-byte MMA steps this chunk holds
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks) {
             if (!FULL && ks >= n_ks) break;
-            const uint64_t a_desc = make_sdesc(sa + ks * 32u, 16u, 1024u);
-            uint64_t b_desc;
-            if (!TRANS_W) {
-              // MN-major B: step (kc * EPR + ks * UMMA_K) rows of 128 bytes into the weight tile
-              const uint32_t k_row = (uint32_t)kc * EPR + (uint32_t)ks * (32u / ES);
-              b_desc = make_sdesc(sw + k_row * 128u, (uint32_t)p.k_dim * 128u, TF32 ? 512u : 1024u, TF32 ? 1u : 2u);
-            } else {
-              b_desc = make_sdesc(sw + (uint32_t)kc * ((uint32_t)p.n_dim * 128u) + ks * 32u, 16u, 1024u);
-            }
-            mma_ss<TF32>(d_tmem, a_desc, b_desc, idesc, (kc | ks) != 0);
+            // A (K-major): 32 bytes further along the row per step.  B: MN-major (forward) steps 32 / ES rows of
+            // 128 bytes, K-major (dgrad) 32 bytes along the row.
+            mma_ss<TF32>(d_tmem, a_desc_s + (uint64_t)(ks * 2), b_desc_kc + (uint64_t)((uint32_t)ks * b_ks_step), idesc, (kc | ks) != 0);
           }
           mma_commit(smem_u32(&sh->empty[s]));
           if (kc == kch - 1) {

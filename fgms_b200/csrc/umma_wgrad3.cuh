@@ -226,6 +226,15 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     const uint32_t sbo = TF32 ? 512u : 1024u, ltype = TF32 ? 1u : 2u;
     const uint32_t mtile_stride = (uint32_t)ES * lbo;  // a 128-row tile spans 128 * ES / 128 pieces
     const uint32_t last_lbo = cfg.alias ? 0u : lbo;
+    // Descriptors of stage 0 at K step 0 (A: one per row tile); all others differ only in the start-address field
+    // (address >> 4, no carry out of it), so the issue loop adds small integers instead of rebuilding them
+    const uint32_t stage0 = smem_u32(sStage);
+    const uint64_t b_desc0 = make_sdesc(stage0 + a_bytes, lbo, sbo, ltype);
+    uint64_t a_desc0[2];
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+      a_desc0[mt] = make_sdesc(stage0 + (uint32_t)mt * mtile_stride, mt + 1 == cfg.n_mtile ? last_lbo : lbo, sbo, ltype);
+    const uint32_t ks_step = (uint32_t)UK * 8u;  // UK contraction rows of 128 bytes, in 16-byte units
     G3Walk cur;
     cur.init(tile_start, n_seg, t0);
     int s = 0, sg = 0, run_i = 0, cur_seg = -1;
@@ -251,16 +260,13 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
       if (lane == 0) {
         fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
         tc_fence_after();
-        const uint32_t sa = smem_u32(sStage + (size_t)s * stage_bytes);
-        const uint32_t sb = sa + a_bytes;
+        const uint64_t s_off = (uint64_t)((uint32_t)s * (stage_bytes >> 4));
+        const uint32_t d0 = tmem_base + (uint32_t)buf * buf_cols;
         for (int ks = 0; ks < pb / UK; ++ks) {
-          const uint32_t kadv = (uint32_t)ks * UK * 128u;
-          const uint64_t b_desc = make_sdesc(sb + kadv, lbo, sbo, ltype);
-          for (int mt = 0; mt < cfg.n_mtile; ++mt) {
-            const uint64_t a_desc = make_sdesc(sa + kadv + mt * mtile_stride, mt + 1 == cfg.n_mtile ? last_lbo : lbo, sbo, ltype);
-            mma_ss<TF32>(tmem_base + (uint32_t)buf * buf_cols + (uint32_t)(mt * cfg.n_acc), a_desc, b_desc,
-                         mt + 1 == cfg.n_mtile ? idesc_last : idesc_full, !(first && ks == 0));
-          }
+          const uint64_t off = s_off + (uint64_t)((uint32_t)ks * ks_step);
+          mma_ss<TF32>(d0, a_desc0[0] + off, b_desc0 + off, cfg.n_mtile == 1 ? idesc_last : idesc_full, !(first && ks == 0));
+          if (cfg.n_mtile == 2)
+            mma_ss<TF32>(d0 + (uint32_t)cfg.n_acc, a_desc0[1] + off, b_desc0 + off, idesc_last, !(first && ks == 0));
         }
         // one commit per group of stages (and one for the CTA's last stage, which nobody waits for)
         if (sg == cfg.group - 1 || t + 1 == t1) mma_commit(smem_u32(&sh->empty[s - sg]));

@@ -10,7 +10,7 @@ from tests.util import TOL, Problem, err
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("name", ["cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4"])
+@pytest.mark.parametrize("name", ["cfg1", "cfg2", "cfg3a", "cfg3b", "cfg4", "cfg5l0"])
 def test_config_parity(name):
     wl = workloads.get(name)
     p = Problem(wl.kmap, wl.c_in, wl.c_out, seed=wl.seed, mode=wl.mode)
