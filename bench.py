@@ -614,20 +614,26 @@ def run_ours(args):
         barrier()
         alone_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
 
-    # per-pass durations (for the roofline of the slowest pass): each kernel alone between two events, right after
-    # the untimed L2 flush (the host has enqueued the call long before the flush ends, so no launch gap is timed)
-    calls = {"fwd": lambda: layer.forward(p.feats, p.weights, out),
-             "dgrad": lambda: backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80),
-             "wgrad": wgrad_kernel_only}
-    for name, call in calls.items():
-        pe = []
-        for _ in range(min(args.steps, 50)):
-            prepare()
-            a, b = ev(), ev()
-            a.record(); call(); b.record()
-            pe.append((a, b))
-        barrier()
-        pass_ms[name] = [a.elapsed_time(b) for a, b in pe]
+    # per-pass durations (for the roofline of the slowest pass): the step's three kernels in the step's order with an
+    # event between them.  The host enqueues the three calls while the untimed flush (about 140 us of device time)
+    # still runs, so no launch gap falls between the events.
+    pe = []
+    for _ in range(min(args.steps, 50)):
+        prepare()
+        e = [ev() for _ in range(4)]
+        e[0].record()
+        layer.forward(p.feats, p.weights, out)
+        e[1].record()
+        backend.fgms_dgrad_cuda(p.grad_out, p.weights, in_grad, p.kpos, p.imap, p.omap, p.arch80)
+        e[2].record()
+        wgrad_kernel_only()
+        e[3].record()
+        pe.append(e)
+    barrier()
+    for e in pe:
+        pass_ms["fwd"].append(e[0].elapsed_time(e[1]))
+        pass_ms["dgrad"].append(e[1].elapsed_time(e[2]))
+        pass_ms["wgrad"].append(e[2].elapsed_time(e[3]))
 
     # warm-L2 variant (no flush), reported beside the headline
     for _ in range(2):
