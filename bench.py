@@ -779,7 +779,10 @@ def run_ours(args):
     # ---- the reference's own CUDA kernels on the same tensors (only where they are sound, only when built) ------
     reference_cuda = None
     if rank == 0 and args.reference_cuda:
-        reference_cuda = run_reference_cuda(wl, p, prepare, ev)
+        try:
+            reference_cuda = run_reference_cuda(wl, p, prepare, ev)
+        except Exception as exc:  # a checker that cannot load or run must not take the benchmark down
+            reference_cuda = {"unavailable": f"the reference extension could not be used: {exc!r}"}
 
     fallbacks = backend.fallback_count() - fallbacks0
     strong = None

@@ -23,7 +23,10 @@ pytestmark = [pytest.mark.gpu, pytest.mark.skipif(not build_ref.available(), rea
 
 
 def _reference_run(p: Problem):
-    ref = build_ref.load()
+    try:
+        ref = build_ref.load()
+    except Exception as exc:  # built for another interpreter or torch: nothing to compare with here
+        pytest.skip(f"the reference extension does not load: {exc!r}")
     torch.cuda.synchronize()
     out = torch.zeros((p.km.n_out, p.c_out), dtype=p.dtype, device="cuda")
     in_grad = torch.zeros((p.km.n_in, p.c_in), dtype=p.dtype, device="cuda")
