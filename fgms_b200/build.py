@@ -17,7 +17,7 @@ LIB = os.path.join(HERE, "libfgms_b200.so")
 SOURCES = [os.path.join(CSRC, "fgms_abi.cu")]
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
-"-Xcompiler", "-fPIC", "-shared", "-cudart", "shared",
+"-Xcompiler", "-fPIC", "-shared", "-cudart", "shared", "-ldl",
 ]
 
 

@@ -11,6 +11,8 @@
 #include <cstring>
 #include <cstdlib>
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 #include "simt_kernels.cuh"
 #include "map_builder.cuh"
@@ -174,6 +176,15 @@ int check_fwd_args(const void* in_feats, const void* kernel, void* out_feats, co
 
 size_t elem_size(int dtype) { return dtype == FGMS_DTYPE_F16 ? 2 : 4; }
 
+// NVTX range named after the entry point, open for the duration of the host call (the enqueue); a timeline tool
+// shows the kernels launched inside it under that name.  Without a tool attached the calls return at once.
+struct TraceRange {
+  explicit TraceRange(const char* name) { nvtxRangePushA(name); }
+  ~TraceRange() { nvtxRangePop(); }
+  TraceRange(const TraceRange&) = delete;
+  TraceRange& operator=(const TraceRange&) = delete;
+};
+
 }  // namespace
 
 extern "C" {
@@ -183,6 +194,7 @@ int fgms_b200_fusion_fwd(const void* in_feats, const void* kernel, void* out_fea
                          const int32_t* out_map, int64_t map_len, int n_in, int n_out, int c_in,
                          int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                          int separate_mid, void* stream) {
+  TraceRange trace_range("fgms_b200_fusion_fwd");
   (void)qkpos;
   if (int rc = check_fwd_args(in_feats, kernel, out_feats, kpos, in_map, out_map, map_len, n_in, n_out, c_in,
                               kernel_c_in, c_out, k_vol, sum_nnz, dtype, math, separate_mid))
@@ -202,6 +214,7 @@ int fgms_b200_seq_fwd(const void* in_feats, const void* kernel, void* out_feats,
                       const int32_t* out_map, int64_t map_len, int n_in, int n_out, int c_in,
                       int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                       int separate_mid, void* stream) {
+  TraceRange trace_range("fgms_b200_seq_fwd");
   if (int rc = check_fwd_args(in_feats, kernel, out_feats, kpos, in_map, out_map, map_len, n_in, n_out, c_in,
                               kernel_c_in, c_out, k_vol, sum_nnz, dtype, math, separate_mid))
     return rc;
@@ -223,6 +236,7 @@ int fgms_b200_seq_fwd(const void* in_feats, const void* kernel, void* out_feats,
 int fgms_b200_dgrad(const void* out_grad, const void* kernel, void* in_grad, const int32_t* kpos,
                     const int32_t* in_map, const int32_t* out_map, int64_t map_len, int n_in, int n_out,
                     int c_in, int c_out, int k_vol, int dtype, int math, void* stream) {
+  TraceRange trace_range("fgms_b200_dgrad");
   if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
   if (int rc = check_math(dtype, math)) return rc;
   if (!kernel || !kpos) return fail(FGMS_ERR_INVALID_ARG, "kernel / kpos must not be null");
@@ -238,6 +252,7 @@ size_t fgms_b200_wgrad_workspace_bytes(int c_in, int c_out, int k_vol, int dtype
 }
 
 int fgms_b200_wgrad_finalize(void* kernel_grad_f16, const void* workspace_f32, int64_t count, void* stream) {
+  TraceRange trace_range("fgms_b200_wgrad_finalize");
   if (count < 0) return fail(FGMS_ERR_INVALID_ARG, "negative count");
   if (count == 0) return FGMS_OK;
   if (!kernel_grad_f16 || !workspace_f32) return fail(FGMS_ERR_INVALID_ARG, "null pointer");
@@ -252,6 +267,7 @@ int fgms_b200_wgrad(const void* in_feats, const void* out_grad, void* kernel_gra
                     const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int64_t map_len,
                     int n_in, int n_out, int c_in, int c_out, int k_vol, int dtype, int math,
                     void* workspace, size_t workspace_bytes, int accumulate_into_kernel_grad, void* stream) {
+  TraceRange trace_range("fgms_b200_wgrad");
   if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
   if (int rc = check_math(dtype, math)) return rc;
   if (!kpos) return fail(FGMS_ERR_INVALID_ARG, "kpos must not be null");
@@ -355,6 +371,7 @@ int fgms_b200_wgrad_f16_noalloc(const void* in_feats, const void* out_grad, void
                                 const int32_t* kpos, const int32_t* in_map, const int32_t* out_map,
                                 int64_t map_len, int n_in, int n_out, int c_in, int c_out, int k_vol,
                                 int math, void* stream) {
+  TraceRange trace_range("fgms_b200_wgrad_f16_noalloc");
   if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
   const long long elems = (long long)k_vol * c_in * c_out;
   if (elems > (long long)FGMS_NOALLOC_MAX_ELEMS)
@@ -374,6 +391,7 @@ int fgms_b200_bwd(const void* out_grad, const void* in_feats, const void* kernel
                   const int32_t* in_map, const int32_t* out_map, int64_t map_len, int n_in, int n_out,
                   int c_in, int kernel_c_in, int c_out, int k_vol, int64_t sum_nnz, int dtype, int math,
                   int separate_mid, void* workspace, size_t workspace_bytes, void* stream) {
+  TraceRange trace_range("fgms_b200_bwd");
   (void)qkpos; (void)separate_mid;
   if (c_in != kernel_c_in)
     return fail(FGMS_ERR_CHANNEL_MISMATCH, "Input feature size and kernel size mismatch");
@@ -439,6 +457,7 @@ int cuda_fail(const char* what) {
 int fgms_b200_build_submanifold_map(const int32_t* coords, int n, int kernel_size, int32_t* kpos, int32_t* in_map,
                                     int32_t* out_map, void* workspace, size_t workspace_bytes, int64_t* pairs_host,
                                     void* stream) {
+  TraceRange trace_range("fgms_b200_build_submanifold_map");
   if (n < 0 || kernel_size < 1 || kernel_size > 7 || kernel_size % 2 == 0)
     return fail(FGMS_ERR_INVALID_ARG, "n must be >= 0 and kernel_size odd, 1..7");
   if (!kpos || (n > 0 && (!coords || !in_map || !out_map))) return fail(FGMS_ERR_INVALID_ARG, "null pointer");
@@ -472,6 +491,7 @@ int fgms_b200_build_submanifold_map(const int32_t* coords, int n, int kernel_siz
 int fgms_b200_build_strided_map(const int32_t* coords, int n, int stride, int32_t* out_coords, int32_t* kpos,
                                 int32_t* in_map, int32_t* out_map, void* workspace, size_t workspace_bytes,
                                 int* n_out_host, void* stream) {
+  TraceRange trace_range("fgms_b200_build_strided_map");
   if (n < 0 || stride < 2 || stride > 4) return fail(FGMS_ERR_INVALID_ARG, "n must be >= 0 and stride 2..4");
   if (!kpos || !n_out_host || (n > 0 && (!coords || !out_coords || !in_map || !out_map)))
     return fail(FGMS_ERR_INVALID_ARG, "null pointer");
@@ -512,6 +532,7 @@ int fgms_b200_build_strided_map(const int32_t* coords, int n, int stride, int32_
 int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int n_in, int k_vol,
                             int64_t pairs, int32_t* kpos_t, int32_t* in_map_t, int32_t* out_map_t, void* workspace,
                             size_t workspace_bytes, void* stream) {
+  TraceRange trace_range("fgms_b200_transpose_map");
   if (n_in < 0 || k_vol < 1 || pairs < 0) return fail(FGMS_ERR_INVALID_ARG, "negative size");
   if (!kpos || !kpos_t || (pairs > 0 && (!in_map || !out_map || !in_map_t || !out_map_t)))
     return fail(FGMS_ERR_INVALID_ARG, "null pointer");
@@ -539,6 +560,7 @@ size_t fgms_b200_peer_exchange_flag_bytes(int world) {
 int fgms_b200_peer_exchange(const float* const* sums, float* const* reduced, uint32_t* const* flags, int rank,
                             int world, int64_t count, uint32_t epoch, int64_t wait_limit_cycles, int ctas,
                             void* stream) {
+  TraceRange trace_range("fgms_b200_peer_exchange");
   if (world < 1 || world > fgms::PX_MAX_WORLD) return fail(FGMS_ERR_INVALID_ARG, "world %d outside [1, %d]", world, fgms::PX_MAX_WORLD);
   if (rank < 0 || rank >= world) return fail(FGMS_ERR_INVALID_ARG, "rank %d outside [0, %d)", rank, world);
   if (count < 0 || count % 4 != 0) return fail(FGMS_ERR_INVALID_ARG, "count must be a non-negative multiple of 4");

@@ -24,6 +24,10 @@
  * Kernels are enqueued on `stream` (a cudaStream_t passed as void*; NULL = legacy default
  * stream, which is what the reference always uses, backend/spconv.cu:73) and the call
  * returns without synchronising, like the reference.
+ *
+ * Every entry point that launches work opens an NVTX range named after itself for the duration of the
+ * host call, so that a timeline tool shows forward / dgrad / wgrad / exchange by name; without a tool
+ * attached the range calls return at once.
  */
 #ifndef FGMS_B200_H_
 #define FGMS_B200_H_
