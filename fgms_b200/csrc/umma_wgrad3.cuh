@@ -134,26 +134,37 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     // ------------------------------------------------------------------ producers
     const int pw = w3_producer_index(warp);
     const int rpw = pb / W3_PROD_WARPS;  // rows of a stage owned by this warp: 4, 8, 16 or 32
-    const int n_pass = rpw >> 2;         // a warp-wide copy covers 4 rows x 128 bytes
     const uint8_t* feats = static_cast<const uint8_t*>(p.feats);
     const uint8_t* og = static_cast<const uint8_t*>(p.out_grad);
     const uint32_t a_row_bytes = (uint32_t)p.c_in * ES, b_row_bytes = (uint32_t)p.c_out * ES;
+    // `lpr` lanes share a row, one 16-byte chunk each: 8 when the longer of the two rows exceeds 64 bytes, 4 / 2
+    // for rows of at most 64 / 32 bytes, so that a warp-wide copy of short rows still carries 32 chunks (8 / 16
+    // rows instead of 4).  The time of a stage's copies goes with the number of warp-wide copy rounds, not with
+    // the bytes they carry.
+    const uint32_t max_row = a_row_bytes > b_row_bytes ? a_row_bytes : b_row_bytes;
+    int lpr = (FULL || max_row > 64) ? 8 : (max_row > 32 ? 4 : 2);
+    if (32 / lpr > rpw) lpr = 8;         // fewer rows per warp than such a round would cover
+    const int rpp = 32 / lpr;            // rows per round: 4, 8 or 16
+    const int n_pass = rpw / rpp;        // rounds per stage: 1 .. 8
+    // Lane (rs, c) = (lane / lpr, lane % lpr) copies 16-byte chunk c of every 128-byte piece of the rows
+    // rs, rs + rpp, ... of the warp's block: one shuffle and one address per row, then one cp.async per
+    // piece at a fixed distance (128 bytes in global memory, `lbo` in shared memory).
+    const int rs = lane / lpr, cc = lane % lpr;
     // 128-byte pieces of a row this lane's 16-byte chunk exists in (the last piece of a row that is no whole
     // number of pieces is filled in part): 0 .. 8
-    const int nha = FULL ? (int)a_row_bytes / 128 : ((int)a_row_bytes - (lane & 7) * 16 + 127) / 128;
-    const int nhb = FULL ? (int)b_row_bytes / 128 : ((int)b_row_bytes - (lane & 7) * 16 + 127) / 128;
-    // Lane (rs, c) = (lane / 8, lane % 8) copies 16-byte chunk c of every 128-byte piece of the rows
-    // rs, rs + 4, ... of the warp's block: one shuffle and one address per row, then one cp.async per
-    // piece at a fixed distance (128 bytes in global memory, `lbo` in shared memory).
-    const int rs = lane >> 3, cc = lane & 7;
-    // piece 0 of row rs + 4 u, relative to the operand's start in the stage: rows 8 apart are 1024 bytes apart in
-    // both layouts, so two offsets (u even / odd) and a multiple of 1024 give all of them
+    const int nha = FULL ? (int)a_row_bytes / 128 : ((int)a_row_bytes - cc * 16 + 127) / 128;
+    const int nhb = FULL ? (int)b_row_bytes / 128 : ((int)b_row_bytes - cc * 16 + 127) / 128;
+    // piece 0 of row rs + rpp u, relative to the operand's start in the stage: rows 8 apart are 1024 bytes apart in
+    // both layouts, so with 4 rows per round two offsets (u even / odd) and a multiple of 1024 give all of them,
+    // with 8 or 16 rows per round one offset and a multiple of 1024 or 2048
     uint32_t dst_rel[2];
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
       const uint32_t row = (uint32_t)(pw * rpw + rs + 4 * u);
       dst_rel[u] = TF32 ? mnmajor32_offset(row, (uint32_t)cc * 16u, lbo, 512u) : mnmajor_offset(row, (uint32_t)cc * 16u, lbo, 1024u);
     }
+    const bool four = rpp == 4;
+    const uint32_t u_step = four ? 1024u : (uint32_t)(rpp >> 3) * 1024u;
     const uint8_t* feats_c = feats + cc * 16;
     const uint8_t* og_c = og + cc * 16;
     // lane r < rpw fetches both map entries of the warp's row r (-1 beyond the stage)
@@ -199,12 +210,12 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
         if (u < n_pass) {
-          const int ia = __shfl_sync(0xffffffffu, cur_a, rs + 4 * u);
-          const int ib = __shfl_sync(0xffffffffu, cur_b, rs + 4 * u);
+          const int ia = __shfl_sync(0xffffffffu, cur_a, rs + rpp * u);
+          const int ib = __shfl_sync(0xffffffffu, cur_b, rs + rpp * u);
           const uint32_t na = ia >= 0 ? 16u : 0u, nb = ib >= 0 ? 16u : 0u;  // 0 bytes read: the chunk is zero-filled
           const uint8_t* pa = feats_c + (size_t)max(ia, 0) * a_row_bytes;
           const uint8_t* pb_ = og_c + (size_t)max(ib, 0) * b_row_bytes;
-          const uint32_t rel = dst_rel[u & 1] + (uint32_t)(u >> 1) * 1024u;
+          const uint32_t rel = four ? dst_rel[u & 1] + (uint32_t)(u >> 1) * 1024u : dst_rel[0] + (uint32_t)u * u_step;
           const uint32_t da = sa + rel, db = sb + rel;
 #pragma unroll
           for (int h = 0; h < 8; ++h)
