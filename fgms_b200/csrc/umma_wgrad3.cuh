@@ -51,6 +51,7 @@ constexpr int W3_SHARED_BYTES = (sizeof(W3Shared) + 15) & ~15;
 
 struct W3Config {
   int pb;         // pairs per stage: 32, 64, 128 or 256
+  int pack;       // pairs whose rows share one 128-byte staged row: 1, or 2 / 4 when both rows are at most 64 / 32 bytes
   int n_mtile;    // 1 or 2 accumulator row tiles: all of 128 rows but possibly the last
   int last_m;     // rows of the last tile's MMA: 128, or 64 when at most 64 rows remain
   int alias;      // 1: the last tile's second piece is its first one read again (descriptor LBO = 0) instead of a
@@ -82,8 +83,9 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int pb = cfg.pb, n_stage = cfg.n_stage;
-  const uint32_t a_bytes = (uint32_t)pb * 128u * cfg.pa;
-  const uint32_t stage_bytes = (uint32_t)pb * 128u * (cfg.pa + cfg.pbp);
+  const int kr = pb / cfg.pack;  // staged rows (contraction steps) per stage
+  const uint32_t a_bytes = (uint32_t)kr * 128u * cfg.pa;
+  const uint32_t stage_bytes = (uint32_t)kr * 128u * (cfg.pa + cfg.pbp);
   uint8_t* sStage = smem;
   uint8_t* sPatch = sStage + (size_t)n_stage * stage_bytes;
   W3Shared* sh = reinterpret_cast<W3Shared*>(sPatch + W3_PATCH_BYTES);
@@ -93,7 +95,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_seg = p.k_vol + 1;
   volatile int* abort_flag = &sh->abort_flag;
-  const uint32_t lbo = (uint32_t)pb * 128u;  // next 128 bytes of every gathered row
+  const uint32_t lbo = (uint32_t)kr * 128u;  // next 128 bytes of every staged row
   const uint32_t buf_cols = (uint32_t)(cfg.n_mtile * cfg.n_acc);
 
   if (tid == 0) {
@@ -158,12 +160,18 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     // both layouts, so with 4 rows per round two offsets (u even / odd) and a multiple of 1024 give all of them,
     // with 8 or 16 rows per round one offset and a multiple of 1024 or 2048
     uint32_t dst_rel[2];
+    const int pack = cfg.pack;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      const uint32_t row = (uint32_t)(pw * rpw + rs + 4 * u);
-      dst_rel[u] = TF32 ? mnmajor32_offset(row, (uint32_t)cc * 16u, lbo, 512u) : mnmajor_offset(row, (uint32_t)cc * 16u, lbo, 1024u);
+      // Packed stages: pair j of the stage sits in staged row j / pack at byte (j % pack) * (128 / pack).  A round
+      // then advances by rpp / pack = 4 staged rows (8 pairs of 64-byte rows, 16 pairs of 32-byte rows), the same
+      // two-offset pattern as unpacked rounds of 4 rows.
+      const uint32_t j = (uint32_t)(pw * rpw + rs) + (uint32_t)(pack > 1 ? rpp : 4) * u;
+      const uint32_t row = j / (uint32_t)pack;
+      const uint32_t byte = (j % (uint32_t)pack) * (128u / (uint32_t)pack) + (uint32_t)cc * 16u;
+      dst_rel[u] = TF32 ? mnmajor32_offset(row, byte, lbo, 512u) : mnmajor_offset(row, byte, lbo, 1024u);
     }
-    const bool four = rpp == 4;
+    const bool four = rpp == 4 || pack > 1;
     const uint32_t u_step = four ? 1024u : (uint32_t)(rpp >> 3) * 1024u;
     const uint8_t* feats_c = feats + cc * 16;
     const uint8_t* og_c = og + cc * 16;
@@ -273,7 +281,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
         tc_fence_after();
         const uint64_t s_off = (uint64_t)((uint32_t)s * (stage_bytes >> 4));
         const uint32_t d0 = tmem_base + (uint32_t)buf * buf_cols;
-        for (int ks = 0; ks < pb / UK; ++ks) {
+        for (int ks = 0; ks < kr / UK; ++ks) {
           const uint64_t off = s_off + (uint64_t)((uint32_t)ks * ks_step);
           mma_ss<TF32>(d0, a_desc0[0] + off, b_desc0 + off, cfg.n_mtile == 1 ? idesc_last : idesc_full, !(first && ks == 0));
           if (cfg.n_mtile == 2)
@@ -299,6 +307,14 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     uint8_t* patch = sPatch + warp * 4096;
     const uint32_t sw7 = (uint32_t)(lane & 7);
     const uint32_t ch = (uint32_t)(lane & 7), rsub = (uint32_t)(lane >> 3);
+    // Packed stages: staged row k holds `pack` pairs side by side, in A and in B alike, so the 64-row accumulator
+    // is pack x pack blocks of `slot` x `slot` elements of which the diagonal ones are sums over pairs (block (s, s):
+    // the pairs in position s) and the others mix two pairs' rows and are dropped.  A warp's 16 rows lie in one
+    // block row; it adds columns [col_base, col_base + c_out) of its rows to gradient rows (row - col_base).
+    // (tf32: the 64-row MMA reads the 32 staged elements twice, rows 32 .. 63 repeat rows 0 .. 31 and are dropped.)
+    const int slot = cfg.pack > 1 ? (128 / cfg.pack) / ES : 0;
+    const bool blk_ok = cfg.pack == 1 || warp * 16 < cfg.pack * slot;
+    const int col_base = (cfg.pack > 1 && blk_ok) ? (warp * 16) / slot * slot : 0;
     int run_i = 0;
     int t = t0;
     while (t < t1 && ok) {
@@ -320,7 +336,8 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
 #pragma unroll
             for (int q = 0; q < 4; ++q) {  // 16 columns at a time: few registers in flight
               uint32_t v[16], h[8];
-              tmem_ld16(taddr + c0 + 16 * q, v);
+              if (cfg.pack > 1 && 16 * q >= slot) break;  // the block's columns end here
+              tmem_ld16(taddr + col_base + c0 + 16 * q, v);
               tmem_ld_wait();
 #pragma unroll
               for (int k = 0; k < 8; ++k) h[k] = pack_half2(__uint_as_float(v[2 * k]), __uint_as_float(v[2 * k + 1]));
@@ -333,7 +350,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
               const uint32_t r = rsub + 4 * u;
               int m;
               if (m128) m = mt * 128 + warp * 32 + (int)r;
-              else m = r < 16 ? mt * 128 + warp * 16 + (int)r : -1;
+              else m = (r < 16 && blk_ok) ? mt * 128 + warp * 16 + (int)r - col_base : -1;
               const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
               if (m >= 0 && m < p.c_in && c0 + (int)(ch << 3) < p.c_out) red_add_h8(dwk16 + (size_t)m * p.c_out + c0 + (ch << 3), v.x, v.y, v.z, v.w);
             }
@@ -346,8 +363,13 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
         const bool m128 = mt + 1 < cfg.n_mtile || cfg.last_m == 128;
         for (int c0 = 0; c0 < p.c_out; c0 += 32) {
           uint32_t v0[16], v1[16];
-          tmem_ld16(taddr + c0, v0);
-          tmem_ld16(taddr + c0 + 16, v1);
+          tmem_ld16(taddr + col_base + c0, v0);
+          if (cfg.pack == 1 || slot > 16) {
+            tmem_ld16(taddr + col_base + c0 + 16, v1);
+          } else {  // the block has 16 columns: the next ones belong to another block (or to no accumulator at all)
+#pragma unroll
+            for (int k = 0; k < 16; ++k) v1[k] = 0u;
+          }
           tmem_ld_wait();
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
@@ -361,7 +383,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
             // M = 128: lane r of warp w is row 32 w + r; M = 64: row i lives in lane (i / 16) * 32 + i % 16
             int m;
             if (m128) m = mt * 128 + warp * 32 + (int)r;
-            else m = r < 16 ? mt * 128 + warp * 16 + (int)r : -1;
+            else m = (r < 16 && blk_ok) ? mt * 128 + warp * 16 + (int)r - col_base : -1;
             const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
             if (m >= 0 && m < p.c_in && c0 + (int)(ch << 2) < p.c_out)
               red_add_v4(dwk + (size_t)m * p.c_out + c0 + (ch << 2), __uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
@@ -400,11 +422,16 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   if (buf_cols > 512) return false;
   cfg->n_buf = 4 * buf_cols <= 512 ? 4 : (2 * buf_cols <= 512 ? 2 : 1);
   cfg->buf_shift = cfg->n_buf == 4 ? 2 : (cfg->n_buf == 2 ? 1 : 0);
-  // pairs per stage: 4, 8 or 16 rows per producer warp
+  // Rows of at most 64 / 32 bytes (both operands): 2 / 4 pairs share a staged row, which halves / quarters the
+  // MMAs per pair — an MMA of 64 x 64 x 16 costs what one of 128 x 128 x 16 does, and with such rows the issue loop
+  // is what bounds the kernel.  The accumulator then holds pack x pack blocks; the epilogue keeps the diagonal.
+  const int max_row = (c_in > c_out ? c_in : c_out) * es;
+  cfg->pack = max_row <= 32 ? 4 : (max_row <= 64 ? 2 : 1);
+  // pairs per stage: 4, 8, 16 or 32 rows per producer warp (packed stages: always 32, the stage is small)
   int pb = W3_MAX_PB;
   const int fixed = 1024 + W3_PATCH_BYTES + W3_SHARED_BYTES + (((2 * k_vol + 3) * 4 + 15) & ~15);
-  const int row_bytes = 128 * (cfg->pa + cfg->pbp);
-  while (pb > 32 && (max_smem - fixed) / (pb * row_bytes) < 3) pb >>= 1;  // keep at least three stages in flight
+  const int row_bytes = 128 * (cfg->pa + cfg->pbp) / cfg->pack;  // staged bytes per pair
+  while (cfg->pack == 1 && pb > 32 && (max_smem - fixed) / (pb * row_bytes) < 3) pb >>= 1;  // keep at least three stages in flight
   int n_stage = (max_smem - fixed) / (pb * row_bytes);
   if (n_stage > W3_MAX_STAGES) n_stage = W3_MAX_STAGES;
   if (n_stage < 2) return false;
