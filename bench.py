@@ -50,7 +50,9 @@ UNIT = "TFLOPS"
 # dram__bytes_read.sum + dram__bytes_write.sum of ONE launch of the named pass on the named workload, from
 # ncu captures of this benchmark's own command; reported only for exactly that pass and workload.
 NCU_TRAFFIC = {
-    ("fwd", "cfg4"): 79.8e6, ("dgrad", "cfg4"): 79.4e6, ("wgrad", "cfg4"): 83.7e6,
+    ("fwd", "cfg4"): 79.5e6, ("dgrad", "cfg4"): 79.3e6, ("wgrad", "cfg4"): 81.7e6,
+    ("fwd", "cfg2"): 33.5e6, ("dgrad", "cfg2"): 33.5e6, ("wgrad", "cfg2"): 33.5e6,
+    ("fwd", "cfg5l0"): 24.6e6, ("dgrad", "cfg5l0"): 24.6e6, ("wgrad", "cfg5l0"): 24.6e6,
 }
 
 
