@@ -34,6 +34,9 @@ SIGNATURES = {
                                             c_size_t, c_void_p, c_void_p]),
     "fgms_b200_transpose_map": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_size_t, c_void_p]),
+    "fgms_b200_neighbor_table_bytes": (c_size_t, [c_int, c_int]),
+    "fgms_b200_build_neighbor_table": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "fgms_b200_fwd_output_stationary": (c_int, [c_void_p] * 4 + [c_int] * 7 + [c_void_p, c_int, c_int, c_void_p]),
     "fgms_b200_peer_exchange_flag_bytes": (c_size_t, [c_int]),
     "fgms_b200_peer_exchange": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int64, ctypes.c_uint32, c_int64, c_int, c_void_p]),
     "fgms_b200_kernel_family": (c_int, [c_int] * 6),

@@ -26,7 +26,7 @@ from . import _lib
 
 __all__ = ["fgms_fusion_fwd_cuda", "fgms_fwd_cuda", "fgms_bwd_cuda", "fgms_dgrad_cuda", "fgms_wgrad_cuda",
            "wgrad_workspace", "wgrad_finalize", "fgms_wgrad_noalloc_cuda", "kernel_family", "fallback_count",
-           "device_status", "launch_count"]
+           "device_status", "launch_count", "build_neighbor_table", "fgms_fwd_os_cuda"]
 
 _L = _lib.lib
 
@@ -117,6 +117,51 @@ def fgms_fusion_fwd_cuda(in_feats, kernel, sum_nnz, out_feats, kpos, qkpos, in_m
             _ptr(in_feats), _ptr(kernel), _ptr(out_feats), _ptr(kpos), _ptr(qkpos), _ptr(in_map), _ptr(out_map),
             in_map.numel(), in_feats.size(0), out_feats.size(0), in_feats.size(1), kernel.size(1), kernel.size(2),
             k_vol, int(sum_nnz), dtype, math, int(bool(separate_mid)), _stream()))
+
+
+def build_neighbor_table(kpos, in_map, out_map, n_in: int, n_out: int):
+    """Neighbour table of the output-stationary forward from the flat pair list: ``nbr[k, r]`` = input row of
+    output row ``r`` under offset ``k`` or -1, an int32 tensor ``[k_vol, n_out rounded up to 128]``
+    (``fgms_b200_build_neighbor_table``).  Every output row may occur at most once per offset."""
+    k_vol = kpos.numel() - 1
+    _check_index("kpos", kpos, in_map.device, k_vol + 1)
+    _check_index("in_map", in_map, in_map.device, None)
+    _check_index("out_map", out_map, in_map.device, in_map.numel())
+    nbytes = _L.fgms_b200_neighbor_table_bytes(int(n_out), k_vol)
+    nbr = torch.empty((k_vol, nbytes // 4 // k_vol), dtype=torch.int32, device=in_map.device)
+    with torch.cuda.device(in_map.device):
+        _lib.check(_L.fgms_b200_build_neighbor_table(_ptr(kpos), _ptr(in_map), _ptr(out_map), in_map.numel(), int(n_in),
+                                                     int(n_out), k_vol, _ptr(nbr), nbytes, _stream()))
+    return nbr
+
+
+def fgms_fwd_os_cuda(in_feats, kernel, out_feats, nbr, arch80, bias=None, relu=False, accumulate=False):
+    """Output-stationary forward (``fgms_b200_fwd_output_stationary``): every output row is computed in one
+    accumulator over all offsets and written once — the same bits on every run, with ``bias`` and ReLU applied on
+    the way out; ``accumulate=True`` adds to ``out_feats`` as the reference's forward does
+    (``backend/spconv.cu:23-246``) and takes neither.  ``nbr`` comes from :func:`build_neighbor_table`.
+    Tensor-core shapes only (``ValueError`` otherwise)."""
+    _check_feat("in_feats", in_feats, None)
+    _check_feat("kernel", kernel, in_feats.dtype, dim=3)
+    _check_feat("out_feats", out_feats, in_feats.dtype)
+    if kernel.size(1) != in_feats.size(1):
+        raise ValueError("Input feature size and kernel size mismatch")
+    if out_feats.size(1) != kernel.size(2):
+        raise ValueError("out_feats width differs from the kernel's output channels")
+    k_vol = kernel.size(0)
+    stride = (out_feats.size(0) + 127) // 128 * 128
+    if nbr.dtype != torch.int32 or not nbr.is_contiguous() or nbr.device != in_feats.device or nbr.numel() != k_vol * stride:
+        raise ValueError("nbr must be the contiguous int32 table build_neighbor_table returns for these sizes")
+    if bias is not None:
+        _check_feat("bias", bias, in_feats.dtype, dim=1)
+        if bias.numel() != kernel.size(2):
+            raise ValueError("bias length differs from the kernel's output channels")
+    dtype, math = _dtype_math(in_feats, arch80)
+    with torch.cuda.device(in_feats.device):
+        _lib.check(_L.fgms_b200_fwd_output_stationary(
+            _ptr(in_feats), _ptr(kernel), _ptr(out_feats), _ptr(nbr), in_feats.size(0), out_feats.size(0),
+            in_feats.size(1), kernel.size(2), k_vol, dtype, math, _ptr(bias), int(bool(relu)), int(bool(accumulate)),
+            _stream()))
 
 
 def fgms_fwd_cuda(in_feats, kernel, sum_nnz, out_feats, kernel_nnz, kernel_pos, in_map, out_map,

@@ -19,6 +19,7 @@
 #include "umma_gms3.cuh"
 #include "umma_wgrad3.cuh"
 #include "peer_exchange.cuh"
+#include "umma_osfwd.cuh"
 
 namespace {
 
@@ -588,6 +589,61 @@ int fgms_b200_peer_exchange(const float* const* sums, float* const* reduced, uin
   }
   fgms::peer_exchange_kernel<<<ctas, fgms::PX_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(p);
   return check_launch("peer_exchange_kernel");
+}
+
+size_t fgms_b200_neighbor_table_bytes(int n_out, int k_vol) {
+  if (n_out < 0 || k_vol < 1) return 0;
+  return (size_t)k_vol * (((size_t)n_out + fgms::OS_TILE - 1) / fgms::OS_TILE * fgms::OS_TILE) * sizeof(int32_t);
+}
+
+int fgms_b200_build_neighbor_table(const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int64_t map_len,
+                                   int n_in, int n_out, int k_vol, int32_t* nbr, size_t nbr_bytes, void* stream) {
+  TraceRange trace_range("fgms_b200_build_neighbor_table");
+  if (n_in < 0 || n_out < 0 || k_vol < 1 || k_vol > 4096) return fail(FGMS_ERR_INVALID_ARG, "negative row count or k_vol outside [1, 4096]");
+  if (!kpos) return fail(FGMS_ERR_INVALID_ARG, "kpos must not be null");
+  if (int rc = check_maps(in_map, out_map, map_len)) return rc;
+  const size_t need = fgms_b200_neighbor_table_bytes(n_out, k_vol);
+  if (need == 0) return FGMS_OK;
+  if (!nbr || nbr_bytes < need) return fail(FGMS_ERR_WORKSPACE, "neighbour table needs %zu bytes", need);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  cudaError_t e = cudaMemsetAsync(nbr, 0xFF, need, st);  // -1 everywhere: no neighbour
+  if (e != cudaSuccess) return fail(FGMS_ERR_CUDA, "cudaMemsetAsync: %s", cudaGetErrorString(e));
+  if (map_len == 0) return FGMS_OK;
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  const long long stride = (long long)(need / sizeof(int32_t) / (size_t)k_vol);
+  long long blocks = (map_len + 255) / 256;
+  if (blocks > 4ll * di.sms) blocks = 4ll * di.sms;
+  fgms::os_fill_nbr_kernel<<<(int)blocks, 256, (size_t)(k_vol + 1) * sizeof(int), st>>>(kpos, in_map, out_map, (long long)map_len,
+                                                                                         n_in, n_out, k_vol, stride, nbr);
+  return check_launch("os_fill_nbr_kernel");
+}
+
+int fgms_b200_fwd_output_stationary(const void* in_feats, const void* kernel, void* out_feats, const int32_t* nbr,
+                                    int n_in, int n_out, int c_in, int c_out, int k_vol, int dtype, int math,
+                                    const void* bias, int relu, int accumulate, void* stream) {
+  TraceRange trace_range("fgms_b200_fwd_output_stationary");
+  if (int rc = check_dims(n_in, n_out, c_in, c_out, k_vol)) return rc;
+  if (int rc = check_math(dtype, math)) return rc;
+  if (!kernel) return fail(FGMS_ERR_INVALID_ARG, "kernel must not be null");
+  if ((n_in > 0 && !in_feats) || (n_out > 0 && (!out_feats || !nbr))) return fail(FGMS_ERR_INVALID_ARG, "feature or table pointer is null");
+  if (accumulate && (bias || relu)) return fail(FGMS_ERR_INVALID_ARG, "bias / ReLU apply to a finished row: not with accumulate");
+  if (n_out == 0) return FGMS_OK;
+  DeviceInfo di;
+  if (int rc = device_info(&di)) return rc;
+  if (!plan_gms(false, c_in, c_out, k_vol, dtype, math, di.max_smem_optin))
+    return fail(FGMS_ERR_UNSUPPORTED, "the output-stationary forward exists for the tensor-core shapes only "
+                "(tf32 / fp16 arithmetic, channel counts multiples of 16 up to 256)");
+  fgms::OsParams p;
+  p.src = in_feats; p.weights = kernel; p.dst = out_feats; p.nbr = nbr; p.bias = bias;
+  p.n_tiles = (n_out + fgms::OS_TILE - 1) / fgms::OS_TILE;
+  p.nbr_stride = (long long)p.n_tiles * fgms::OS_TILE;
+  p.n_in = n_in; p.n_out = n_out; p.c_in = c_in; p.c_out = c_out; p.k_vol = k_vol;
+  p.relu = relu ? 1 : 0; p.accumulate = accumulate ? 1 : 0;
+  const int rc = fgms::launch_umma_osfwd(p, dtype == FGMS_DTYPE_F16, static_cast<cudaStream_t>(stream), di.sms, di.max_smem_optin);
+  if (rc == 0) return check_launch("umma_osfwd_kernel");
+  if (rc < 0) return fail(FGMS_ERR_CUDA, "umma_osfwd_kernel setup failed (%d)", rc);
+  return fail(FGMS_ERR_INVALID_ARG, "tensors must be 16-byte aligned");
 }
 
 int64_t fgms_b200_device_status(int reset) {

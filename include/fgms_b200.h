@@ -190,6 +190,32 @@ int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const in
                             int32_t* out_map_t, void* workspace, size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------------------------
+ * Output-stationary forward.  The reference's forward (backend/spconv.cu:23-246, epilogue
+ * backend/fwd_kernels.cuh:130-141) and fgms_b200_fusion_fwd add every pair's product to its output row with an
+ * atomic: up to k_vol atomics per row in an order that differs from run to run, and nothing can be applied to the
+ * finished row inside the kernel.  This entry point computes each output row in one accumulator instead and
+ * writes it once, so the result is the same bits on every run and bias + ReLU are applied on the way out:
+ *
+ *     out[r] = act( sum_k in[nbr[k][r]] * W[k] + bias )      (accumulate = 0)
+ *     out[r] += sum_k in[nbr[k][r]] * W[k]                    (accumulate = 1: the reference's contract; no bias, no ReLU)
+ *
+ * It takes the map as a neighbour table: nbr[k * stride + r] = input row of output row r under offset k, or -1,
+ * stride = n_out rounded up to a multiple of 128, fgms_b200_neighbor_table_bytes(n_out, k_vol) bytes in all.
+ * fgms_b200_build_neighbor_table fills it from the flat pair list (kpos entries are clamped to map_len, pairs
+ * with an entry outside the tensors are skipped and counted); the pair list must hold every output row at most
+ * once per offset, as every valid kernel map does.  Tensor-core shapes only (tf32 / f16 math, channel counts
+ * multiples of 16 up to 256): FGMS_ERR_UNSUPPORTED otherwise.  `bias`: c_out values of the storage type or
+ * NULL.  Cost: one 128-row stage per (128 output rows, offset) however few of those rows have a neighbour
+ * there, against one per 128 pairs in the scatter form: slower on sparse clouds, the form to use for dense
+ * ones or where reproducible bits or the fused epilogue matter. */
+size_t fgms_b200_neighbor_table_bytes(int n_out, int k_vol);
+int fgms_b200_build_neighbor_table(const int32_t* kpos, const int32_t* in_map, const int32_t* out_map, int64_t map_len,
+                                   int n_in, int n_out, int k_vol, int32_t* nbr, size_t nbr_bytes, void* stream);
+int fgms_b200_fwd_output_stationary(const void* in_feats, const void* kernel, void* out_feats, const int32_t* nbr,
+                                    int n_in, int n_out, int c_in, int c_out, int k_vol, int dtype, int math,
+                                    const void* bias, int relu, int accumulate, void* stream);
+
+/* ---------------------------------------------------------------------------------------------
  * Multi-GPU: sum of the ranks' fp32 weight-gradient partial sums over peer memory.  No counterpart in the
  * reference (it has no multi-GPU path); it stands where a data-parallel caller would otherwise issue an
  * all-reduce of the [k_vol, c_in, c_out] fp32 sums that fgms_b200_wgrad leaves in its workspace.

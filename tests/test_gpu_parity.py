@@ -101,6 +101,25 @@ def test_k_vol_one_and_empty_offsets(mode):
     _check_all(Problem(km, 64, 128, seed=6, mode=mode))
 
 
+@pytest.mark.parametrize("mode", ["fp16", "tf32"])
+@pytest.mark.parametrize("c_in,c_out", [(16, 16), (16, 32), (32, 16), (32, 32)])
+def test_short_rows_full_and_partial_stages(mode, c_in, c_out):
+    # rows of at most 64 bytes: the weight-gradient kernel stages several pairs to one 128-byte row.  One offset
+    # of 1000 pairs = three whole 256-pair stages and a partial one; then a map whose offsets hold 1 .. 5 pairs.
+    n = 1000
+    ident = np.arange(n, dtype=np.int32)
+    perm = np.random.default_rng(1).permutation(n).astype(np.int32)
+    km = maps.KernelMap(n, n, 1, np.array([n], np.int32), np.array([0, n], np.int32), perm, ident)
+    _check_all(Problem(km, c_in, c_out, seed=11, mode=mode))
+    knnz = np.array([1, 0, 5, 2, 0, 3, 1, 4], np.int32)
+    kpos = np.concatenate([[0], np.cumsum(knnz)]).astype(np.int32)
+    rng = np.random.default_rng(2)
+    imap = np.concatenate([rng.permutation(40)[:c] for c in knnz]).astype(np.int32)
+    omap = np.concatenate([rng.permutation(30)[:c] for c in knnz]).astype(np.int32)
+    km = maps.KernelMap(40, 30, 8, knnz, kpos, imap, omap)
+    _check_all(Problem(km, c_in, c_out, seed=12, mode=mode))
+
+
 @pytest.mark.parametrize("mode", MODES)
 def test_empty_cloud_and_no_pairs(mode):
     km = maps.build_submanifold_map(np.zeros((0, 3), np.int32))
