@@ -674,6 +674,43 @@ def run_ours(args):
         pass_ms["dgrad"].append(e[1].elapsed_time(e[2]))
         pass_ms["wgrad"].append(e[2].elapsed_time(e[3]))
 
+    # ---- the output-stationary forward beside the scatter form (one rank, tensor-core shapes) ----------------
+    out_stationary = None
+    if world == 1 and backend.kernel_family("fwd", wl.c_in, wl.c_out, p.dtype, p.arch80, km.k_vol) == "tcgen05":
+        tb = [ev(), ev()]
+        tb[0].record()
+        nbr = backend.build_neighbor_table(p.kpos, p.imap, p.omap, km.n_in, km.n_out)
+        tb[1].record()
+        os_out = torch.empty_like(out)
+        for _ in range(3):
+            backend.fgms_fwd_os_cuda(p.feats, p.weights, os_out, nbr, p.arch80)
+        oe = []
+        for _ in range(min(args.steps, 20)):
+            flush()
+            e = [ev(), ev()]
+            e[0].record()
+            backend.fgms_fwd_os_cuda(p.feats, p.weights, os_out, nbr, p.arch80)
+            e[1].record()
+            oe.append(e)
+        torch.cuda.synchronize()
+        first = os_out.clone()
+        backend.fgms_fwd_os_cuda(p.feats, p.weights, os_out, nbr, p.arch80)
+        out.zero_()
+        layer.forward(p.feats, p.weights, out)
+        torch.cuda.synchronize()
+        n_tiles = (km.n_out + 127) // 128
+        out_stationary = {
+            "what": "forward with one accumulator per output row over all offsets, each row written once (no atomics, "
+                    "bias / ReLU fusable); one 128-row stage per (128 output rows, offset) whatever the number of pairs in it",
+            "fwd_ms": statistics.mean(a.elapsed_time(b) for a, b in oe),
+            "scatter_fwd_ms": statistics.mean(pass_ms["fwd"]),
+            "stages": n_tiles * km.k_vol, "scatter_stages": (km.pairs + 127) // 128,
+            "table_build_ms": tb[0].elapsed_time(tb[1]),
+            "same_bits_on_a_second_run": bool(torch.equal(first, os_out)),
+            "max_abs_diff_vs_scatter_form": float((os_out.float() - out.float()).abs().max()),
+        }
+        del nbr, os_out, first
+
     # warm-L2 variant (no flush), reported beside the headline
     for _ in range(2):
         out.zero_(); in_grad.zero_(); w_grad.zero_(); step(False)
@@ -896,6 +933,7 @@ def run_ours(args):
             "ms_per_step_l2_warm": warm_ms / k,
             "pairs_all_ranks": pairs_all,
             "map_builder": map_builder,
+            **({"output_stationary": out_stationary} if out_stationary else {}),
         }
         if world > 1:
             line["pass_ms"]["wgrad_kernel"] = line["pass_ms"]["wgrad"]

@@ -13,8 +13,9 @@
 // by offset, so that a weight matrix is staged once per group of tiles and offset.
 //
 // The price is one 128-row stage per (tile, offset) however few of the tile's rows have a neighbour there:
-// k_vol stages per 128 output rows against pairs / 128 stages in the scatter form.  It pays for dense clouds
-// and wherever determinism or a fused epilogue is worth more than the extra stages.
+// k_vol stages per 128 output rows against pairs / 128 stages in the scatter form — measured 1.0-1.4 times the
+// scatter form's time on fully occupied grids, 3.4 times at 9.5 pairs per voxel, 8 times at 2.1.  It is the form
+// for callers to whom reproducible bits or the fused epilogue are worth the extra stages.
 //
 // Roles (13 warps): 8 producers (16-byte cp.async gathers into the K-major 128-byte-swizzled stage ring, weight
 // matrices into one of two buffers), one MMA warp, 4 epilogue warps.  All waits are bounded.
