@@ -151,3 +151,24 @@ def test_reserved_sm_setting_validates():
     assert L.fgms_b200_set_reserved_sms(65) == _lib.ERR_INVALID_ARG
     assert L.fgms_b200_set_reserved_sms(8) == _lib.OK
     assert L.fgms_b200_set_reserved_sms(0) == _lib.OK
+
+
+def test_output_stationary_forward_validates_without_a_device():
+    L = _lib.lib
+    assert L.fgms_b200_neighbor_table_bytes(0, 27) == 0
+    assert L.fgms_b200_neighbor_table_bytes(1, 27) == 27 * 128 * 4
+    assert L.fgms_b200_neighbor_table_bytes(146546, 27) == 27 * 146560 * 4
+    p = 256  # never dereferenced: validation fails first
+    build = lambda kpos, imap, omap, map_len, nbr, nbytes, k_vol=27: L.fgms_b200_build_neighbor_table(
+        kpos, imap, omap, map_len, 10, 10, k_vol, nbr, nbytes, None)
+    assert build(None, p, p, 4, p, 1 << 20) == _lib.ERR_INVALID_ARG
+    assert build(p, None, p, 4, p, 1 << 20) == _lib.ERR_INVALID_ARG
+    assert build(p, p, p, 4, p, 16) == _lib.ERR_WORKSPACE
+    assert build(p, p, p, 4, p, 1 << 20, k_vol=0) == _lib.ERR_INVALID_ARG
+    fwd = lambda dtype, math, bias=None, relu=0, acc=0, c_in=32, nbr=p: L.fgms_b200_fwd_output_stationary(
+        p, p, p, nbr, 10, 10, c_in, 32, 27, dtype, math, bias, relu, acc, None)
+    assert fwd(_lib.DTYPE_F16, _lib.MATH_TF32) == _lib.ERR_UNSUPPORTED
+    assert fwd(_lib.DTYPE_F16, _lib.MATH_F16, bias=p, acc=1) == _lib.ERR_INVALID_ARG and "accumulate" in _lib.last_error()
+    assert fwd(_lib.DTYPE_F16, _lib.MATH_F16, relu=1, acc=1) == _lib.ERR_INVALID_ARG
+    assert fwd(_lib.DTYPE_F16, _lib.MATH_F16, nbr=None) == _lib.ERR_INVALID_ARG
+    assert fwd(_lib.DTYPE_F16, _lib.MATH_F16, c_in=0) == _lib.ERR_INVALID_ARG
