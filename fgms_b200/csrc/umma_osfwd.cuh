@@ -13,8 +13,8 @@
 // by offset, so that a weight matrix is staged once per group of tiles and offset.
 //
 // The price is one 128-row stage per (tile, offset) however few of the tile's rows have a neighbour there:
-// k_vol stages per 128 output rows against pairs / 128 stages in the scatter form — measured 1.0-1.4 times the
-// scatter form's time on fully occupied grids, 3.4 times at 9.5 pairs per voxel, 8 times at 2.1.  It is the form
+// k_vol stages per 128 output rows against pairs / 128 stages in the scatter form — measured 0.9-1.05 times the
+// scatter form's time on fully occupied grids, 2.6 times at 9.5 pairs per voxel, 8 times at 2.1.  It is the form
 // for callers to whom reproducible bits or the fused epilogue are worth the extra stages.
 //
 // Roles (13 warps): 8 producers (16-byte cp.async gathers into the K-major 128-byte-swizzled stage ring, weight
@@ -59,24 +59,26 @@ struct OsShared {
 };
 constexpr int OS_SHARED_BYTES = (sizeof(OsShared) + 15) & ~15;
 
-// The walk every role makes: groups of `gsz` tiles; within a group offset by offset, within an offset tile by tile.
+// The walk every role makes over the CTA's tiles [.., t1): groups of up to `gsz` consecutive tiles; within a group
+// offset by offset, within an offset tile by tile.  A CTA's tile range is cut to the tile (not to the group), so the
+// CTAs' loads differ by one tile at most; the last group of a CTA may be smaller.
 struct OsWalk {
-  int grp, k, g, gv;  // group, offset, tile of the group, tiles this group has
-  __device__ __forceinline__ void init(int grp_, int gsz, int n_tiles) {
-    grp = grp_; k = 0; g = 0;
-    gv = min(gsz, n_tiles - grp * gsz);
+  int tb, k, g, gv;  // first tile of the group, offset, tile of the group, tiles this group has (<= 0: past the end)
+  __device__ __forceinline__ void init(int t0, int gsz, int t1) {
+    tb = t0; k = 0; g = 0;
+    gv = min(gsz, t1 - tb);
   }
-  __device__ __forceinline__ void next(int gsz, int n_tiles, int k_vol) {
-    if (++g == gv) {
+  __device__ __forceinline__ void next(int gsz, int t1, int k_vol) {
+    if (++g >= gv) {
       g = 0;
       if (++k == k_vol) {
         k = 0;
-        ++grp;
-        gv = min(gsz, n_tiles - grp * gsz);
+        tb += gsz;
+        gv = min(gsz, t1 - tb);
       }
     }
   }
-  __device__ __forceinline__ int tile(int gsz) const { return grp * gsz + g; }
+  __device__ __forceinline__ int tile() const { return tb + g; }
 };
 
 // nbr[k][out_map[j]] = in_map[j] for every pair j of offset k (the table is filled with -1 beforehand).  Every kpos
@@ -147,12 +149,12 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
   tc_fence_after();
   const uint32_t tmem_base = sh->tmem_base;
 
-  // this CTA's groups of tiles
-  const int n_groups = (p.n_tiles + gsz - 1) / gsz;
-  const int g0 = (int)((long long)blockIdx.x * n_groups / gridDim.x), g1 = (int)((long long)(blockIdx.x + 1) * n_groups / gridDim.x);
+  // this CTA's tiles
+  int t0, t1;
+  cta_tile_range(p.n_tiles, &t0, &t1);
   bool ok = true;
 
-  if (g0 >= g1) {
+  if (t0 >= t1) {
     // nothing for this CTA
   } else if (warp >= OS_PROD_WARP0) {
     // ------------------------------------------------------------------ producers
@@ -172,7 +174,7 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
     // lane r < 16 fetches the neighbour entry of the warp's row r
     auto load_entry = [&](const OsWalk& w) -> int {
       if (lane >= 16) return -1;
-      return __ldg(p.nbr + (long long)w.k * p.nbr_stride + (long long)w.tile(gsz) * OS_TILE + 16 * pw + lane);
+      return __ldg(p.nbr + (long long)w.k * p.nbr_stride + (long long)w.tile() * OS_TILE + 16 * pw + lane);
     };
     // weight matrix W_k -> MN-major operand (rows = contraction index), as in the scatter-form forward
     const int cpr = p.c_out * ES / 16;  // 16-byte chunks per row of W_k
@@ -190,22 +192,22 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
     };
 
     OsWalk cur, pf;
-    cur.init(g0, gsz, p.n_tiles);
+    cur.init(t0, gsz, t1);
     pf = cur;
     int e[OS_PREFETCH];
 #pragma unroll
     for (int d = 0; d < OS_PREFETCH; ++d) {
-      e[d] = pf.grp < g1 ? load_entry(pf) : -1;
-      pf.next(gsz, p.n_tiles, p.k_vol);
+      e[d] = pf.tb < t1 ? load_entry(pf) : -1;
+      pf.next(gsz, t1, p.k_vol);
     }
     int s = 0, n_load = -1, wb = 0;
     uint32_t ph = 0;
-    while (cur.grp < g1 && ok) {
+    while (cur.tb < t1 && ok) {
       int ent = e[0];
 #pragma unroll
       for (int d = 0; d + 1 < OS_PREFETCH; ++d) e[d] = e[d + 1];
-      e[OS_PREFETCH - 1] = pf.grp < g1 ? load_entry(pf) : -1;
-      pf.next(gsz, p.n_tiles, p.k_vol);
+      e[OS_PREFETCH - 1] = pf.tb < t1 ? load_entry(pf) : -1;
+      pf.next(gsz, t1, p.k_vol);
       if ((unsigned)ent >= (unsigned)p.n_in) {
         if (ent != -1) report_problem();  // an entry outside the tensor: treated as no neighbour, counted
         ent = -1;
@@ -241,7 +243,7 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
         cp_async_arrive_noinc(smem_u32(&sh->full[s]));
         if (++s == n_stage) { s = 0; ph ^= 1u; }
       }
-      cur.next(gsz, p.n_tiles, p.k_vol);
+      cur.next(gsz, t1, p.k_vol);
     }
   } else if (warp == OS_MMA_WARP) {
     // ------------------------------------------------------------------ MMA issuer
@@ -251,11 +253,11 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
     const uint32_t b_kc_step = (uint32_t)EPR * 8u;        // one 128-byte K chunk further, in 16-byte units
     const uint32_t b_ks_step = (32u / ES) * 8u;           // one 32-byte MMA step further
     OsWalk cur;
-    cur.init(g0, gsz, p.n_tiles);
-    int s = 0, n_load = -1, wb = 0, grp_i = 0, last_grp = g0;
+    cur.init(t0, gsz, t1);
+    int s = 0, n_load = -1, wb = 0, grp_i = 0, last_tb = t0;
     uint32_t ph = 0;
-    while (cur.grp < g1 && ok) {
-      if (cur.grp != last_grp) { last_grp = cur.grp; ++grp_i; }
+    while (cur.tb < t1 && ok) {
+      if (cur.tb != last_tb) { last_tb = cur.tb; ++grp_i; }
       if (cur.g == 0) {
         ++n_load;
         wb = (cfg.n_wbuf == 2) ? (n_load & 1) : 0;
@@ -290,7 +292,7 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
         __syncwarp();
         if (++s == n_stage) { s = 0; ph ^= 1u; }
       }
-      cur.next(gsz, p.n_tiles, p.k_vol);
+      cur.next(gsz, t1, p.k_vol);
     }
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0-3)
@@ -304,13 +306,13 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
     const uint32_t sw7 = (uint32_t)(lane & 7);
     const uint32_t ch = (uint32_t)(lane & 7), rsub = (uint32_t)(lane >> 3);
     int grp_i = 0;
-    for (int grp = g0; grp < g1 && ok; ++grp, ++grp_i) {
-      const int gv = min(gsz, p.n_tiles - grp * gsz);
+    for (int tb = t0; tb < t1 && ok; tb += gsz, ++grp_i) {
+      const int gv = min(gsz, t1 - tb);
       for (int g = 0; g < gv && ok; ++g) {
         ok = g3_wait(&sh->tmem_full[g], (uint32_t)grp_i & 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
-        const int row0 = (grp * gsz + g) * OS_TILE + 32 * warp;  // output row of this warp's lane 0
+        const int row0 = (tb + g) * OS_TILE + 32 * warp;  // output row of this warp's lane 0
         const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + (uint32_t)(g * cfg.n_acc);
         for (uint32_t cb = 0; cb < row_bytes; cb += 128) {
           const uint32_t vb = min(128u, row_bytes - cb);  // bytes of this block that belong to the row
@@ -404,8 +406,7 @@ inline int launch_umma_osfwd(const OsParams& p, bool f16, cudaStream_t st, int s
     return 1;
   G3Config cfg;
   if (!g3_plan(p.c_in, p.c_out, f16 ? 2 : 4, p.k_vol, max_smem, false, &cfg)) return 1;
-  const int n_groups = (p.n_tiles + cfg.n_tbuf - 1) / cfg.n_tbuf;
-  const int grid = n_groups < sms ? n_groups : sms;
+  const int grid = p.n_tiles < sms ? p.n_tiles : sms;
   if (grid <= 0) return 0;
   if (f16) {
     static std::atomic<int> granted[64];
