@@ -16,7 +16,7 @@ import torch
 
 from . import backend
 
-__all__ = ["sparse_conv", "SparseConv3d", "SparseUNet"]
+__all__ = ["sparse_conv", "sparse_conv_inference", "SparseConv3d", "SparseUNet"]
 
 
 class _SparseConvFunction(torch.autograd.Function):
@@ -47,6 +47,28 @@ def sparse_conv(feats: torch.Tensor, weight: torch.Tensor, kmap, arch80: bool = 
     if weight.size(0) != kmap.kpos.numel() - 1:
         raise ValueError("weight and kernel map disagree on the number of offsets")
     return _SparseConvFunction.apply(feats, weight, kmap.kpos, kmap.imap, kmap.omap, kmap.n_out, arch80)
+
+
+def sparse_conv_inference(feats: torch.Tensor, weight: torch.Tensor, kmap, bias: torch.Tensor | None = None,
+                          relu: bool = False, arch80: bool = True) -> torch.Tensor:
+    """Forward only, through the output-stationary kernel (``backend.fgms_fwd_os_cuda``): every output row is
+    written once — the same bits on every run — with ``bias`` and ReLU applied in the kernel's epilogue (a
+    batch-norm layer in inference form is a scaled weight and a bias).  No autograd.  The neighbour table the
+    kernel reads is built on first use and kept on ``kmap``.  Tensor-core shapes only (fp16, or fp32 storage
+    with tf32 arithmetic; channel counts multiples of 16 up to 256)."""
+    if feats.size(0) != kmap.n_in:
+        raise ValueError(f"feats has {feats.size(0)} rows, the kernel map expects {kmap.n_in}")
+    nbr = getattr(kmap, "_neighbor_table", None)
+    if nbr is None:
+        nbr = backend.build_neighbor_table(kmap.kpos, kmap.imap, kmap.omap, kmap.n_in, kmap.n_out)
+        try:
+            kmap._neighbor_table = nbr
+        except AttributeError:  # a map type without room for it: rebuilt on every call
+            pass
+    out = torch.empty((kmap.n_out, weight.size(2)), dtype=feats.dtype, device=feats.device)
+    with torch.no_grad():
+        backend.fgms_fwd_os_cuda(feats.contiguous(), weight.detach().contiguous(), out, nbr, arch80, bias=bias, relu=relu)
+    return out
 
 
 class SparseConv3d(torch.nn.Module):

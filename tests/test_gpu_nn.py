@@ -48,3 +48,20 @@ def test_two_layers_share_a_map_and_train():
             for q in params:
                 q -= 0.5 * q.grad
     assert losses[2] < losses[1] < losses[0]
+
+
+def test_inference_form_matches_the_autograd_form_with_bias_and_relu():
+    """conv + bias + ReLU in one kernel (output-stationary forward) against the same three steps with the scatter
+    form; the table is built once and kept on the map; two calls give identical bits."""
+    from fgms_b200 import gpu_maps, nn
+    torch.manual_seed(1)
+    coords = clouds.uniform_cloud(3000, 20, 5)
+    dk = gpu_maps.build_submanifold_map(torch.from_numpy(coords).cuda(), 3)
+    layer = nn.SparseConv3d(64, 32, dtype=torch.float16)
+    x = torch.randn((dk.n_in, 64), device="cuda").half()
+    bias = (torch.randn(32, device="cuda") * 0.3).half()
+    ref = torch.relu(layer(x, dk).detach().float() + bias.float())
+    got = nn.sparse_conv_inference(x, layer.weight, dk, bias=bias, relu=True)
+    assert hasattr(dk, "_neighbor_table")
+    assert float((got.float() - ref).abs().max()) <= 1e-2 * max(float(ref.abs().max()), 1e-6)
+    assert torch.equal(got, nn.sparse_conv_inference(x, layer.weight, dk, bias=bias, relu=True))
