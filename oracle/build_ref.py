@@ -11,7 +11,7 @@ the reference is sound (fp16 128 -> 128 submanifold: fused forward ``_fgms_fusio
 ``_fgms_fusion_fp16_W_transpose_v2``, wgrad ``_fgms_fusion_fp16_I_transpose_v4``).  It is never loaded by the
 product package.
 
-    python -m oracle.build_ref [--force]          (needs the reference checkout: FGMS_REFERENCE_DIR or /root/reference)
+    python -m oracle.build_ref [--force]          (needs the reference checkout: FGMS_REFERENCE_DIR, or the default below)
 """
 from __future__ import annotations
 

@@ -13,7 +13,7 @@ Two variants:
 * CPU: the same harness with a stand-in ``FGMS.backend`` that answers with the CPU oracle on CPU tensors.  It
   proves the harness and pins the oracle once more against the reference's own loops, without a GPU.
 
-Both need a checkout of the reference (``FGMS_REFERENCE_DIR``, default ``/root/reference``) and are skipped without
+Both need a checkout of the reference (``FGMS_REFERENCE_DIR``, or the default of ``REF`` below) and are skipped without
 one: its scripts are not copied into this repository.
 """
 import contextlib
