@@ -318,6 +318,9 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
     int s = 0;
     uint32_t ph = 0;
     int cur_w = -1, n_load = -1, wb = 0, tile_i = 0;
+    // One lane runs the whole loop — waits, issue, commits — so that no warp-wide hand-shake sits between a
+    // stage landing and its MMAs; the other lanes wait at the end.
+    if (lane == 0)
     for (int t = t0; t < t1 && ok; ++t, ++tile_i) {
       const int buf = tile_i & (cfg.n_tbuf - 1);
       const uint32_t use = (uint32_t)tile_i >> cfg.tbuf_shift;
@@ -329,15 +332,15 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
       }
       cur.next(tile_start, n_seg);
       const bool last_of_w = (t + 1 == t1) || g3_widx(cur, p) != cur_w;
-      ok = g3_wait(&sh->tmem_empty[buf], (use & 1u) ^ 1u, abort_flag);
+      ok = mbar_wait(smem_u32(&sh->tmem_empty[buf]), (use & 1u) ^ 1u, abort_flag);
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + (uint32_t)(buf * cfg.n_acc);
       const uint64_t b_desc_w = b_desc0 + (uint64_t)((uint32_t)wb * ((uint32_t)cfg.w_bytes >> 4));
       for (int kc = 0; kc < kch && ok; ++kc) {
-        ok = g3_wait(&sh->full[s], ph, abort_flag);
+        ok = mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag);
         if (!ok) break;
-        if (lane == 0) {
+        {
           fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
           tc_fence_after();
           const uint64_t a_desc_s = a_desc0 + (uint64_t)((uint32_t)s * (G3_STAGE_BYTES >> 4));
@@ -356,10 +359,11 @@ __global__ void __launch_bounds__(G3_THREADS, 1) umma_gms3_kernel(GmsParams p, G
             if (last_of_w) mma_commit(smem_u32(&sh->w_free[wb]));
           }
         }
-        __syncwarp();
         if (++s == n_stage) { s = 0; ph ^= 1u; }
       }
     }
+    __syncwarp();
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0-7)
     // Two groups of four warps take alternate tiles, so that one group's TMEM reads and conversions run

@@ -256,6 +256,8 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
     cur.init(t0, gsz, t1);
     int s = 0, n_load = -1, wb = 0, grp_i = 0, last_tb = t0;
     uint32_t ph = 0;
+    // one lane runs the whole loop (waits, issue, commits); the other lanes wait at the end
+    if (lane == 0)
     while (cur.tb < t1 && ok) {
       if (cur.tb != last_tb) { last_tb = cur.tb; ++grp_i; }
       if (cur.g == 0) {
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
       }
       if (cur.k == 0) {
         // first offset of the group: the accumulator must have been drained by the epilogue of the previous group
-        ok = g3_wait(&sh->tmem_empty[cur.g], ((uint32_t)grp_i & 1u) ^ 1u, abort_flag);
+        ok = mbar_wait(smem_u32(&sh->tmem_empty[cur.g]), ((uint32_t)grp_i & 1u) ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
       }
@@ -272,9 +274,9 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
       const uint64_t b_desc_w = b_desc0 + (uint64_t)((uint32_t)wb * ((uint32_t)cfg.w_bytes >> 4));
       const bool last_k = cur.k == p.k_vol - 1, last_of_w = cur.g == cur.gv - 1;
       for (int kc = 0; kc < kch && ok; ++kc) {
-        ok = g3_wait(&sh->full[s], ph, abort_flag);
+        ok = mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag);
         if (!ok) break;
-        if (lane == 0) {
+        {
           fence_proxy_async();
           tc_fence_after();
           const uint64_t a_desc_s = a_desc0 + (uint64_t)((uint32_t)s * (G3_STAGE_BYTES >> 4));
@@ -289,11 +291,12 @@ __global__ void __launch_bounds__(OS_THREADS, 1) umma_osfwd_kernel(OsParams p, G
             if (last_of_w) mma_commit(smem_u32(&sh->w_free[wb]));
           }
         }
-        __syncwarp();
         if (++s == n_stage) { s = 0; ph ^= 1u; }
       }
       cur.next(gsz, t1, p.k_vol);
     }
+    __syncwarp();
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
   } else {
     // ------------------------------------------------------------------ epilogue (warps 0-3)
     // Warp q owns TMEM lanes 32 q .. 32 q + 31 = tile rows 32 q + lane.  16 accumulator columns at a time:

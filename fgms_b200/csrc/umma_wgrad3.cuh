@@ -259,24 +259,26 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     int s = 0, sg = 0, run_i = 0, cur_seg = -1;
     uint32_t ph = 0;
     bool first = true;
+    // One lane runs the whole loop — waits, issue, commits — so that no warp-wide hand-shake sits between a
+    // stage landing and its MMAs; the other lanes wait at the end.
+    if (lane == 0) {
     for (int t = t0; t < t1 && ok; ++t) {
       if (cur.seg != cur_seg) {
         if (cur_seg >= 0) {
-          if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[run_i & (cfg.n_buf - 1)]));
-          __syncwarp();
+          mma_commit(smem_u32(&sh->tmem_full[run_i & (cfg.n_buf - 1)]));
           ++run_i;
         }
         cur_seg = cur.seg;
         first = true;
         const uint32_t use = (uint32_t)run_i >> cfg.buf_shift;
-        ok = g3_wait(&sh->tmem_empty[run_i & (cfg.n_buf - 1)], (use & 1u) ^ 1u, abort_flag);
+        ok = mbar_wait(smem_u32(&sh->tmem_empty[run_i & (cfg.n_buf - 1)]), (use & 1u) ^ 1u, abort_flag);
         if (!ok) break;
         tc_fence_after();
       }
       const int buf = run_i & (cfg.n_buf - 1);
-      ok = g3_wait(&sh->full[s], ph, abort_flag);
+      ok = mbar_wait(smem_u32(&sh->full[s]), ph, abort_flag);
       if (!ok) break;
-      if (lane == 0) {
+      {
         fence_proxy_async();  // the stage was written through cp.async; the MMA reads it through the async proxy
         tc_fence_after();
         const uint64_t s_off = (uint64_t)((uint32_t)s * (stage_bytes >> 4));
@@ -290,16 +292,15 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
         // one commit per group of stages (and one for the CTA's last stage, which nobody waits for)
         if (sg == cfg.group - 1 || t + 1 == t1) mma_commit(smem_u32(&sh->empty[s - sg]));
       }
-      __syncwarp();
       first = false;
       if (++sg == cfg.group) sg = 0;
       if (++s == n_stage) { s = 0; ph ^= 1u; }
       cur.next(tile_start, n_seg);
     }
-    if (ok && cur_seg >= 0) {
-      if (lane == 0) mma_commit(smem_u32(&sh->tmem_full[run_i & (cfg.n_buf - 1)]));
-      __syncwarp();
+    if (ok && cur_seg >= 0) mma_commit(smem_u32(&sh->tmem_full[run_i & (cfg.n_buf - 1)]));
     }
+    __syncwarp();
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
   } else if (warp < W3_EPI_WARPS) {
     // ------------------------------------------------------------------ epilogue (warps 0-3)
     // Thread (warp, lane) holds accumulator row m in its TMEM lane.  32 columns of the warp's 32 rows
