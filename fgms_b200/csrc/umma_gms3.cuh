@@ -75,12 +75,11 @@ struct G3Config {
   int smem;     // dynamic shared memory of the launch
 };
 
-// one lane polls, the warp learns the outcome
+// Every lane probes the barrier itself (one broadcast read per probe, and each lane's own acquire orders its later
+// reads); one vote makes the outcome the warp's, so that a wait that ran out takes the whole warp out of its loop.
 __device__ __forceinline__ bool g3_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  int ok = 1;
-  if ((threadIdx.x & 31) == 0) ok = umma::mbar_wait(umma::smem_u32(bar), parity, abort_flag) ? 1 : 0;
-  __syncwarp();  // orders the other lanes' later reads after what lane 0's acquire made visible
-  return __shfl_sync(0xffffffffu, ok, 0) != 0;
+  const bool ok = umma::mbar_wait(umma::smem_u32(bar), parity, abort_flag);
+  return __all_sync(0xffffffffu, ok) != 0;
 }
 
 // Walks consecutive tiles of the tile table without searching: the segment only ever moves forward.

@@ -13,7 +13,7 @@
 // by offset, so that a weight matrix is staged once per group of tiles and offset.
 //
 // The price is one 128-row stage per (tile, offset) however few of the tile's rows have a neighbour there:
-// k_vol stages per 128 output rows against pairs / 128 stages in the scatter form — measured 0.9-1.05 times the
+// k_vol stages per 128 output rows against pairs / 128 stages in the scatter form — measured 0.9-1.1 times the
 // scatter form's time on fully occupied grids, 2.6 times at 9.5 pairs per voxel, 8 times at 2.1.  It is the form
 // for callers to whom reproducible bits or the fused epilogue are worth the extra stages.
 //

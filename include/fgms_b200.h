@@ -206,7 +206,7 @@ int fgms_b200_transpose_map(const int32_t* kpos, const int32_t* in_map, const in
  * once per offset, as every valid kernel map does.  Tensor-core shapes only (tf32 / f16 math, channel counts
  * multiples of 16 up to 256): FGMS_ERR_UNSUPPORTED otherwise.  `bias`: c_out values of the storage type or
  * NULL.  Cost: one 128-row stage per (128 output rows, offset) however few of those rows have a neighbour
- * there, against one per 128 pairs in the scatter form.  Measured on a B200 (fp16): 0.9 - 1.05 times the scatter
+ * there, against one per 128 pairs in the scatter form.  Measured on a B200 (fp16): 0.9 - 1.1 times the scatter
  * form's time (with the zeroing of the output that form needs) on fully occupied grids (26 pairs per voxel), 2.6
  * times on an indoor surface (9.5 pairs per voxel), 8 times on a LiDAR sweep (2.1 pairs per voxel): the form to use where reproducible bits or the fused
  * epilogue are worth that. */
