@@ -141,9 +141,10 @@ class PeerExchange:
         self.device = torch.device(device)
         self.count = (int(count) + 3) // 4 * 4
         self.group = group
-        # CTAs of 128 threads and 32 registers; few enough to be resident all at once beside a persistent kernel
-        # (one per SM at most): one CTA per 2048 values of the buffer, between 16 and 128
-        self.ctas = int(ctas) if ctas else max(16, min(128, self.count // 2048))
+        # CTAs of 128 threads and 32 registers, one per 2048 values of the buffer: between 16 and 128 (at most one per
+        # SM, resident all at once beside a persistent kernel) for buffers of up to 4 MB; up to 512 for larger ones,
+        # which are bound by the bytes in flight over the link (a few of these CTAs fit an SM beside a persistent one)
+        self.ctas = int(ctas) if ctas else max(16, min(128 if self.count <= (1 << 20) else 512, self.count // 2048))
         self.wait_limit = int(wait_limit_cycles)
         if buffers is not None:
             self.rank, self.world, sums, reduced, flags = buffers

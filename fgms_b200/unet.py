@@ -161,19 +161,34 @@ def flat_layout(spec, align: int = 128):
     return where, off
 
 
-def plan_buckets(spec, where, bucket_bytes: int):
+def plan_buckets(spec, where, bucket_bytes: int, tail_bytes: int = 0):
     """Cut the flat buffer into buckets of consecutive layers (backward order), each closed once it holds at least
     ``bucket_bytes`` of fp32 sums (the last one takes what is left).  Returns ``[(first element, one past the last,
     index of the layer whose weight gradient completes the bucket)]``: that layer's gradient is the last of the bucket to
-    be enqueued, so the bucket's exchange can start right after it."""
-    buckets, start, acc = [], 0, 0
+    be enqueued, so the bucket's exchange can start right after it.
+
+    Nothing is left to run beside the exchange of the LAST bucket, so it should be small: with ``tail_bytes`` the
+    layers at the end of the backward (the first layers of the network) whose sums together fit ``tail_bytes`` form
+    a bucket of their own, and only the layers before them are cut greedily."""
     order = list(range(len(spec) - 1, -1, -1))
-    for i in order:
+    size = lambda i: (where[i][1] - where[i][0]) * 4
+    n_tail, acc = 0, 0
+    for i in reversed(order):
+        if tail_bytes <= 0 or acc + size(i) > tail_bytes:
+            break
+        acc += size(i)
+        n_tail += 1
+    head = order[:len(order) - n_tail] if n_tail < len(order) else []
+    tail = order[len(head):]
+    buckets, start, acc = [], 0, 0
+    for i in head:
         lo, hi = where[i]
         acc += (hi - lo) * 4
-        if acc >= bucket_bytes or i == order[-1]:
+        if acc >= bucket_bytes or i == head[-1]:
             buckets.append((start, hi, i))
             start, acc = hi, 0
+    if tail:
+        buckets.append((start, where[tail[-1]][1], tail[-1]))
     return buckets
 
 
@@ -282,7 +297,7 @@ class UNetStep:
             self._w_off[i] = (off, off + sz)
             off += sz
         # buckets: consecutive layers in backward order, closed when they reach `bucket_bytes` of fp32 sums
-        self.buckets = plan_buckets(self.spec, where, bucket_bytes) if self.multi else []
+        self.buckets = plan_buckets(self.spec, where, bucket_bytes, tail_bytes=min(1 << 20, bucket_bytes // 4)) if self.multi else []
 
         # a small fp32 workspace for layers whose weight gradient has no single-launch fp16 form (single rank only)
         self._ws = None

@@ -178,3 +178,21 @@ def test_bucketed_exchange_of_a_stack_on_cpu_ranks(tmp_path):
         lo = where[i][0]
         assert np.allclose(flats[0][lo: lo + n], own[0][pos: pos + n] + own[1][pos: pos + n], rtol=1e-12, atol=1e-12), l.name
         pos += n
+
+
+def test_bucket_plan_keeps_the_last_bucket_small():
+    """Nothing runs beside the last bucket's exchange: with ``tail_bytes`` the network's first layers (the end of the
+    backward) get a bucket of their own that fits it, and the cut still covers the buffer without gaps."""
+    from fgms_b200 import unet
+    spec = unet.minkunet_spec(4, (32, 64, 128, 256))
+    where, total = unet.flat_layout(spec)
+    plain = unet.plan_buckets(spec, where, bucket_bytes=6 << 20)
+    tailed = unet.plan_buckets(spec, where, bucket_bytes=6 << 20, tail_bytes=1 << 20)
+    for b in (plain, tailed):
+        assert b[0][0] == 0 and b[-1][1] == total and all(x[1] == y[0] for x, y in zip(b, b[1:]))
+        assert [last for _, _, last in b] == sorted((last for _, _, last in b), reverse=True)  # backward order
+    assert (tailed[-1][1] - tailed[-1][0]) * 4 <= 1 << 20 < (plain[-1][1] - plain[-1][0]) * 4
+    assert tailed[-1][2] == 0 and len(tailed) == len(plain) + 1
+    # a tail that nothing fits, and one that everything fits
+    assert unet.plan_buckets(spec, where, 6 << 20, tail_bytes=16) == plain
+    assert unet.plan_buckets(spec, where, 6 << 20, tail_bytes=1 << 30) == [(0, total, 0)]

@@ -156,7 +156,8 @@ def test_accumulate_semantics(mode):
     out = p.run_fwd()
     once = out.clone()
     p.run_fwd(out=out)
-    assert err(out, 2.0 * once.float().cpu().numpy().astype(np.float64)) <= 2e-3
+    # fp16: every atomic of the second call rounds at twice the magnitude and in another order than the first
+    assert err(out, 2.0 * once.float().cpu().numpy().astype(np.float64)) <= {"fp32": 1e-5, "tf32": 2e-3, "fp16": 1e-2}[mode]
 
 
 def test_error_behaviour():
