@@ -59,4 +59,6 @@ def test_matches_the_reference_cuda_path(case):
     assert max(ours) <= TOL["fp16"]
     assert max(theirs) <= 3 * TOL["fp16"]   # fp16 accumulation: the reference's own error
     assert max(between) <= 3 * TOL["fp16"]
-    assert max(ours) <= max(theirs) + 1e-4  # fp32 accumulation is at least as close to the exact result
+    # fp32 accumulation is at least as close to the exact result, up to what the order of the fp16 atomics (both
+    # libraries scatter with them) moves either error from run to run
+    assert max(ours) <= max(theirs) + 1e-3
