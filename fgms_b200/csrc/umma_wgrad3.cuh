@@ -51,7 +51,8 @@ constexpr int W3_SHARED_BYTES = (sizeof(W3Shared) + 15) & ~15;
 
 struct W3Config {
   int pb;         // pairs per stage: 32, 64, 128 or 256
-  int pack;       // pairs whose rows share one 128-byte staged row: 1, or 2 / 4 when both rows are at most 64 / 32 bytes
+  int pack;       // pairs that share one staged row (their rows side by side): 1, 2 or 4
+  int slot_a, slot_b;  // packed stages: bytes a pair's row takes in the staged row of A / of B
   int n_mtile;    // 1 or 2 accumulator row tiles: all of 128 rows but possibly the last
   int last_m;     // rows of the last tile's MMA: 128, or 64 when at most 64 rows remain
   int alias;      // 1: the last tile's second piece is its first one read again (descriptor LBO = 0) instead of a
@@ -75,7 +76,8 @@ __device__ __forceinline__ void w3_stage(const G3Walk& w, int pb, const int* kpo
 }
 
 // FULL: both row lengths are whole 128-byte pieces; the producers' copy loops then carry no per-chunk test.
-template <bool TF32, bool FULL>
+// PACKED: several pairs share a staged row (cfg.pack > 1); the unpacked instantiations carry none of its arithmetic.
+template <bool TF32, bool FULL, bool PACKED>
 __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams p, W3Config cfg) {
   using namespace umma;
   constexpr int ES = TF32 ? 4 : 2;
@@ -83,7 +85,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~static_cast<uintptr_t>(1023));
   const int pb = cfg.pb, n_stage = cfg.n_stage;
-  const int kr = pb / cfg.pack;  // staged rows (contraction steps) per stage
+  const int kr = PACKED ? pb / cfg.pack : pb;  // staged rows (contraction steps) per stage
   const uint32_t a_bytes = (uint32_t)kr * 128u * cfg.pa;
   const uint32_t stage_bytes = (uint32_t)kr * 128u * (cfg.pa + cfg.pbp);
   uint8_t* sStage = smem;
@@ -160,19 +162,20 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     // both layouts, so with 4 rows per round two offsets (u even / odd) and a multiple of 1024 give all of them,
     // with 8 or 16 rows per round one offset and a multiple of 1024 or 2048
     uint32_t dst_rel[2];
-    const int pack = cfg.pack;
+    const int pack = PACKED ? cfg.pack : 1;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
-      // Packed stages: pair j of the stage sits in staged row j / pack at byte (j % pack) * (128 / pack).  A round
-      // then advances by rpp / pack = 4 staged rows (8 pairs of 64-byte rows, 16 pairs of 32-byte rows), the same
-      // two-offset pattern as unpacked rounds of 4 rows.
-      const uint32_t j = (uint32_t)(pw * rpw + rs) + (uint32_t)(pack > 1 ? rpp : 4) * u;
-      const uint32_t row = j / (uint32_t)pack;
-      const uint32_t byte = (j % (uint32_t)pack) * (128u / (uint32_t)pack) + (uint32_t)cc * 16u;
-      dst_rel[u] = TF32 ? mnmajor32_offset(row, byte, lbo, 512u) : mnmajor_offset(row, byte, lbo, 1024u);
+      const uint32_t row = (uint32_t)(pw * rpw + rs + 4 * u);
+      dst_rel[u] = TF32 ? mnmajor32_offset(row, (uint32_t)cc * 16u, lbo, 512u) : mnmajor_offset(row, (uint32_t)cc * 16u, lbo, 1024u);
     }
-    const bool four = rpp == 4 || pack > 1;
+    const bool four = rpp == 4;
     const uint32_t u_step = four ? 1024u : (uint32_t)(rpp >> 3) * 1024u;
+    // Packed stages: pair j of the stage sits in staged row j / pack, its rows at byte (j % pack) * slot_a of A and
+    // (j % pack) * slot_b of B (a position beyond 128 bytes is a further piece).  Round u covers the staged row
+    // row0 + u * rpp / pack; the offsets are worked out per round.
+    const uint32_t pk_row0 = (uint32_t)(pw * rpw + rs) / (uint32_t)pack, pk_step = (uint32_t)(rpp / pack);
+    const uint32_t pk_byte_a = (uint32_t)((pw * rpw + rs) % pack) * (uint32_t)cfg.slot_a + (uint32_t)cc * 16u;
+    const uint32_t pk_byte_b = (uint32_t)((pw * rpw + rs) % pack) * (uint32_t)cfg.slot_b + (uint32_t)cc * 16u;
     const uint8_t* feats_c = feats + cc * 16;
     const uint8_t* og_c = og + cc * 16;
     // lane r < rpw fetches both map entries of the warp's row r (-1 beyond the stage)
@@ -223,8 +226,15 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
           const uint32_t na = ia >= 0 ? 16u : 0u, nb = ib >= 0 ? 16u : 0u;  // 0 bytes read: the chunk is zero-filled
           const uint8_t* pa = feats_c + (size_t)max(ia, 0) * a_row_bytes;
           const uint8_t* pb_ = og_c + (size_t)max(ib, 0) * b_row_bytes;
-          const uint32_t rel = four ? dst_rel[u & 1] + (uint32_t)(u >> 1) * 1024u : dst_rel[0] + (uint32_t)u * u_step;
-          const uint32_t da = sa + rel, db = sb + rel;
+          uint32_t rel_a, rel_b;
+          if (!PACKED) {
+            rel_a = rel_b = four ? dst_rel[u & 1] + (uint32_t)(u >> 1) * 1024u : dst_rel[0] + (uint32_t)u * u_step;
+          } else {
+            const uint32_t row = pk_row0 + (uint32_t)u * pk_step;
+            rel_a = TF32 ? mnmajor32_offset(row, pk_byte_a, lbo, 512u) : mnmajor_offset(row, pk_byte_a, lbo, 1024u);
+            rel_b = TF32 ? mnmajor32_offset(row, pk_byte_b, lbo, 512u) : mnmajor_offset(row, pk_byte_b, lbo, 1024u);
+          }
+          const uint32_t da = sa + rel_a, db = sb + rel_b;
 #pragma unroll
           for (int h = 0; h < 8; ++h)
             if (h < nha) cp_async16_n(da + (uint32_t)h * lbo, pa + h * 128, na);
@@ -308,14 +318,17 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
     uint8_t* patch = sPatch + warp * 4096;
     const uint32_t sw7 = (uint32_t)(lane & 7);
     const uint32_t ch = (uint32_t)(lane & 7), rsub = (uint32_t)(lane >> 3);
-    // Packed stages: staged row k holds `pack` pairs side by side, in A and in B alike, so the 64-row accumulator
-    // is pack x pack blocks of `slot` x `slot` elements of which the diagonal ones are sums over pairs (block (s, s):
-    // the pairs in position s) and the others mix two pairs' rows and are dropped.  A warp's 16 rows lie in one
-    // block row; it adds columns [col_base, col_base + c_out) of its rows to gradient rows (row - col_base).
-    // (tf32: the 64-row MMA reads the 32 staged elements twice, rows 32 .. 63 repeat rows 0 .. 31 and are dropped.)
-    const int slot = cfg.pack > 1 ? (128 / cfg.pack) / ES : 0;
-    const bool blk_ok = cfg.pack == 1 || warp * 16 < cfg.pack * slot;
-    const int col_base = (cfg.pack > 1 && blk_ok) ? (warp * 16) / slot * slot : 0;
+    // Packed stages: staged row k holds `pack` pairs side by side, in A and in B, so the accumulator is pack x pack
+    // blocks of slot_m x slot_n elements of which the diagonal ones are sums over pairs (block (s, s): the pairs in
+    // position s) and the others mix two pairs' rows and are dropped.  A warp's rows (32 of a 128-row accumulator,
+    // 16 of a 64-row one) lie in one block row; it adds columns [col_base, col_base + c_out) of its rows to gradient
+    // rows (row - row_base).  (tf32 with at most 32 staged elements: the 64-row MMA reads them twice, rows 32 .. 63
+    // repeat rows 0 .. 31 and are dropped.)
+    const int slot_m = PACKED ? cfg.slot_a / ES : 0, slot_n = PACKED ? cfg.slot_b / ES : 0;
+    const int warp_row0 = (cfg.last_m == 128 ? 32 : 16) * warp;  // packed stages have one row tile
+    const bool blk_ok = !PACKED || warp_row0 < cfg.pack * slot_m;
+    const int blk = (PACKED && blk_ok) ? warp_row0 / slot_m : 0;
+    const int row_base = blk * slot_m, col_base = blk * slot_n;
     int run_i = 0;
     int t = t0;
     while (t < t1 && ok) {
@@ -337,7 +350,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
 #pragma unroll
             for (int q = 0; q < 4; ++q) {  // 16 columns at a time: few registers in flight
               uint32_t v[16], h[8];
-              if (cfg.pack > 1 && 16 * q >= slot) break;  // the block's columns end here
+              if (PACKED && c0 + 16 * q >= slot_n) break;  // the block's columns end here
               tmem_ld16(taddr + col_base + c0 + 16 * q, v);
               tmem_ld_wait();
 #pragma unroll
@@ -350,8 +363,8 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
             for (uint32_t u = 0; u < 8; ++u) {
               const uint32_t r = rsub + 4 * u;
               int m;
-              if (m128) m = mt * 128 + warp * 32 + (int)r;
-              else m = (r < 16 && blk_ok) ? mt * 128 + warp * 16 + (int)r - col_base : -1;
+              if (m128) m = blk_ok ? mt * 128 + warp * 32 + (int)r - row_base : -1;
+              else m = (r < 16 && blk_ok) ? mt * 128 + warp * 16 + (int)r - row_base : -1;
               const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
               if (m >= 0 && m < p.c_in && c0 + (int)(ch << 3) < p.c_out) red_add_h8(dwk16 + (size_t)m * p.c_out + c0 + (ch << 3), v.x, v.y, v.z, v.w);
             }
@@ -365,7 +378,7 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
         for (int c0 = 0; c0 < p.c_out; c0 += 32) {
           uint32_t v0[16], v1[16];
           tmem_ld16(taddr + col_base + c0, v0);
-          if (cfg.pack == 1 || slot > 16) {
+          if (!PACKED || slot_n - c0 > 16) {
             tmem_ld16(taddr + col_base + c0 + 16, v1);
           } else {  // the block has 16 columns: the next ones belong to another block (or to no accumulator at all)
 #pragma unroll
@@ -383,8 +396,8 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
             const uint32_t r = rsub + 4 * u;  // TMEM lane (within the warp's quarter) whose row this is
             // M = 128: lane r of warp w is row 32 w + r; M = 64: row i lives in lane (i / 16) * 32 + i % 16
             int m;
-            if (m128) m = mt * 128 + warp * 32 + (int)r;
-            else m = (r < 16 && blk_ok) ? mt * 128 + warp * 16 + (int)r - col_base : -1;
+            if (m128) m = blk_ok ? mt * 128 + warp * 32 + (int)r - row_base : -1;
+            else m = (r < 16 && blk_ok) ? mt * 128 + warp * 16 + (int)r - row_base : -1;
             const uint4 v = *reinterpret_cast<const uint4*>(patch + r * 128 + ((ch ^ (r & 7)) << 4));
             if (m >= 0 && m < p.c_in && c0 + (int)(ch << 2) < p.c_out)
               red_add_v4(dwk + (size_t)m * p.c_out + c0 + (ch << 2), __uint_as_float(v.x), __uint_as_float(v.y), __uint_as_float(v.z), __uint_as_float(v.w));
@@ -412,27 +425,38 @@ __global__ void __launch_bounds__(W3_THREADS, 1) umma_wgrad3_kernel(WgradParams 
 inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Config* cfg) {
   if (!umma_supported(c_in, c_out, es)) return false;
   const int epr = 128 / es;  // elements per 128-byte piece
-  cfg->n_mtile = (c_in + 127) / 128;
-  const int rem = c_in - 128 * (cfg->n_mtile - 1);
+  // Packed stages: `pack` pairs share a staged row, their rows side by side in A and in B, so one MMA contracts
+  // pack times as many pairs — an MMA of 64 x 64 x 16 costs what one of 128 x 128 x 16 does, and with rows of up to
+  // 128 bytes the issue loop is what bounds the kernel.  The accumulator then holds pack x pack blocks; the epilogue
+  // keeps the diagonal.  Rows of at most 32 / 64 bytes: 4 / 2 pairs in slots of 32 / 64 bytes.  Longer rows whose
+  // lengths are powers of two: 2 pairs, each row its own slot, while both fit one 128-row, 256-column accumulator
+  // (twice, so that two accumulators alternate).
+  const int a_row = c_in * es, b_row = c_out * es, max_row = a_row > b_row ? a_row : b_row;
+  const bool pow2 = (a_row & (a_row - 1)) == 0 && (b_row & (b_row - 1)) == 0;
+  cfg->pack = 1; cfg->slot_a = cfg->slot_b = 0;
+  if (max_row <= 32) { cfg->pack = 4; cfg->slot_a = cfg->slot_b = 32; }
+  else if (max_row <= 64) { cfg->pack = 2; cfg->slot_a = cfg->slot_b = 64; }
+  else if (pow2 && 2 * c_in <= 128 && 2 * c_out <= 256) { cfg->pack = 2; cfg->slot_a = a_row; cfg->slot_b = b_row; }
+  // rows and columns of the accumulator
+  const int m_eff = cfg->pack > 1 ? cfg->pack * cfg->slot_a / es : c_in;
+  const int n_eff = cfg->pack > 1 ? cfg->pack * cfg->slot_b / es : c_out;
+  cfg->n_mtile = (m_eff + 127) / 128;
+  const int rem = m_eff - 128 * (cfg->n_mtile - 1);
   cfg->last_m = rem <= 64 ? 64 : 128;
   cfg->alias = (es == 4 && rem <= 32) ? 1 : 0;
   cfg->pa = (cfg->n_mtile - 1) * es + (cfg->last_m == 128 ? es : es / 2) - cfg->alias;  // a 128-row tile reads 128 / epr = es pieces
-  cfg->n_acc = (c_out + epr - 1) / epr * epr;
+  cfg->n_acc = (n_eff + epr - 1) / epr * epr;
   cfg->pbp = cfg->n_acc / epr;
   const int buf_cols = cfg->n_mtile * cfg->n_acc;
   if (buf_cols > 512) return false;
   cfg->n_buf = 4 * buf_cols <= 512 ? 4 : (2 * buf_cols <= 512 ? 2 : 1);
   cfg->buf_shift = cfg->n_buf == 4 ? 2 : (cfg->n_buf == 2 ? 1 : 0);
-  // Rows of at most 64 / 32 bytes (both operands): 2 / 4 pairs share a staged row, which halves / quarters the
-  // MMAs per pair — an MMA of 64 x 64 x 16 costs what one of 128 x 128 x 16 does, and with such rows the issue loop
-  // is what bounds the kernel.  The accumulator then holds pack x pack blocks; the epilogue keeps the diagonal.
-  const int max_row = (c_in > c_out ? c_in : c_out) * es;
-  cfg->pack = max_row <= 32 ? 4 : (max_row <= 64 ? 2 : 1);
   // pairs per stage: 4, 8, 16 or 32 rows per producer warp (packed stages: always 32, the stage is small)
   int pb = W3_MAX_PB;
   const int fixed = 1024 + W3_PATCH_BYTES + W3_SHARED_BYTES + (((2 * k_vol + 3) * 4 + 15) & ~15);
   const int row_bytes = 128 * (cfg->pa + cfg->pbp) / cfg->pack;  // staged bytes per pair
-  while (cfg->pack == 1 && pb > 32 && (max_smem - fixed) / (pb * row_bytes) < 3) pb >>= 1;  // keep at least three stages in flight
+  // keep at least three stages in flight; a packed stage keeps the producers' round a whole number of staged rows
+  while (pb > (cfg->pack > 1 ? 128 : 32) && (max_smem - fixed) / (pb * row_bytes) < 3) pb >>= 1;
   int n_stage = (max_smem - fixed) / (pb * row_bytes);
   if (n_stage > W3_MAX_STAGES) n_stage = W3_MAX_STAGES;
   if (n_stage < 2) return false;
@@ -446,17 +470,19 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   return true;
 }
 
-template <bool TF32, bool FULL>
+template <bool TF32, bool FULL, bool PACKED>
 inline int w3_launch_as(const WgradParams& p, const W3Config& cfg, cudaStream_t st, int sms, int max_smem) {
   static std::atomic<int> granted[64];
-  if (int rc = ensure_smem(umma_wgrad3_kernel<TF32, FULL>, max_smem, granted)) return rc;
-  return launch_pdl(umma_wgrad3_kernel<TF32, FULL>, sms, W3_THREADS, (size_t)cfg.smem, st, p, cfg) == cudaSuccess ? 0 : -1;
+  if (int rc = ensure_smem(umma_wgrad3_kernel<TF32, FULL, PACKED>, max_smem, granted)) return rc;
+  return launch_pdl(umma_wgrad3_kernel<TF32, FULL, PACKED>, sms, W3_THREADS, (size_t)cfg.smem, st, p, cfg) == cudaSuccess ? 0 : -1;
 }
 template <bool TF32>
 inline int w3_launch(const WgradParams& p, const W3Config& cfg, cudaStream_t st, int sms, int max_smem) {
   const int es = TF32 ? 4 : 2;
   const bool full = (p.c_in * es) % 128 == 0 && (p.c_out * es) % 128 == 0;
-  return full ? w3_launch_as<TF32, true>(p, cfg, st, sms, max_smem) : w3_launch_as<TF32, false>(p, cfg, st, sms, max_smem);
+  if (cfg.pack > 1)
+    return full ? w3_launch_as<TF32, true, true>(p, cfg, st, sms, max_smem) : w3_launch_as<TF32, false, true>(p, cfg, st, sms, max_smem);
+  return full ? w3_launch_as<TF32, true, false>(p, cfg, st, sms, max_smem) : w3_launch_as<TF32, false, false>(p, cfg, st, sms, max_smem);
 }
 
 // 0 launched, 1 the pointers are not 16-byte aligned or the shape has no plan (the caller takes the CUDA-core
