@@ -428,14 +428,15 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   // Packed stages: `pack` pairs share a staged row, their rows side by side in A and in B, so one MMA contracts
   // pack times as many pairs — an MMA of 64 x 64 x 16 costs what one of 128 x 128 x 16 does, and with rows of up to
   // 128 bytes the issue loop is what bounds the kernel.  The accumulator then holds pack x pack blocks; the epilogue
-  // keeps the diagonal.  Rows of at most 32 / 64 bytes: 4 / 2 pairs in slots of 32 / 64 bytes.  Longer rows whose
+  // keeps the diagonal.  Rows of at most 32 / 64 bytes: 4 pairs in slots of 32 / 64 bytes (a 64 x 64 accumulator,
+  // or 128 x 128 for the 64-byte slots of fp16: one MMA per 64 pairs).  Longer rows whose
   // lengths are powers of two: 2 pairs, each row its own slot, while both fit one 128-row, 256-column accumulator
   // (twice, so that two accumulators alternate).
   const int a_row = c_in * es, b_row = c_out * es, max_row = a_row > b_row ? a_row : b_row;
   const bool pow2 = (a_row & (a_row - 1)) == 0 && (b_row & (b_row - 1)) == 0;
   cfg->pack = 1; cfg->slot_a = cfg->slot_b = 0;
   if (max_row <= 32) { cfg->pack = 4; cfg->slot_a = cfg->slot_b = 32; }
-  else if (max_row <= 64) { cfg->pack = 2; cfg->slot_a = cfg->slot_b = 64; }
+  else if (max_row <= 64) { cfg->pack = 4; cfg->slot_a = cfg->slot_b = 64; }
   else if (pow2 && 2 * c_in <= 128 && 2 * c_out <= 256) { cfg->pack = 2; cfg->slot_a = a_row; cfg->slot_b = b_row; }
   // rows and columns of the accumulator
   const int m_eff = cfg->pack > 1 ? cfg->pack * cfg->slot_a / es : c_in;
