@@ -1028,7 +1028,8 @@ def main():
     ap.add_argument("--cfg5-steps", type=int, default=20)
     ap.add_argument("--transport", default="auto", choices=["auto", "peer", "nccl"],
                     help="N > 1: how the weight-gradient sums are exchanged: the library's kernel over peer memory, an NCCL "
-                         "all-reduce, or (auto) the former for the single layer's 1.8 MB and the latter for the stack's 6 MB+ buckets")
+                         "all-reduce, or (auto) the former for the single layer's 1.8 MB and, for the stack's buckets, whichever of "
+                         "NCCL launched eagerly and the library's kernel replayed from a graph a short trial finds faster")
     ap.add_argument("--no-reference-cuda", dest="reference_cuda", action="store_false",
                     help="do not time the reference's CUDA kernels beside this library (they run only when built and sound)")
     args = ap.parse_args()
