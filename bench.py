@@ -24,12 +24,16 @@ configuration the 60 %-of-roofline target is stated on).  The metric is effectiv
                  (``fgms_b200.unet``, 25 layers, fp16), one ~120 k-voxel scene per rank, with the
                  bucketed weight-gradient all-reduce overlapped with the backward when N > 1.
 
+* ``output_stationary``  (N = 1) the forward that writes every output row once, beside the scatter form.
+
 With N > 1 (torchrun, one rank per GPU) every rank holds its own scene of the same kind (weak
-scaling, data parallel); the weight-gradient partial sums are combined with one NCCL all-reduce
-inside the timed step, and the exchanged result is checked on the GPUs after the timed loop
-(``multi_gpu_check``).  Beside it ONE scene is cut over the ranks by output-row range (forward) /
-input-row range (dgrad) and that step is reported as ``strong_scaling`` (``--shard scenes`` skips it).
-Rank 0 prints ONE JSON line.
+scaling, data parallel); the weight-gradient partial sums are exchanged inside the timed step — by
+the library's peer-memory kernel beside the input-gradient kernel, the whole step replayed from one
+CUDA graph (``--transport nccl``: one NCCL all-reduce, eager launches) — and the exchanged result
+is checked on the GPUs after the timed loop (``multi_gpu_check``).  A rendezvous kernel after the
+untimed L2 flush starts every rank's timed step together.  Beside it ONE scene is cut over the ranks
+by output-row range (forward) / input-row range (dgrad) and that step is reported as
+``strong_scaling`` (``--shard scenes`` skips it).  Rank 0 prints ONE JSON line.
 """
 from __future__ import annotations
 
