@@ -69,7 +69,7 @@ def test_golden_fixtures_fp32(golden):
 
 
 @pytest.mark.parametrize("mode", MODES)
-@pytest.mark.parametrize("c_in,c_out", [(1, 1), (3, 5), (4, 32), (16, 16), (16, 32), (32, 16), (17, 33), (32, 32), (32, 64), (64, 32), (64, 64),
+@pytest.mark.parametrize("c_in,c_out", [(1, 1), (3, 5), (4, 32), (16, 16), (16, 32), (32, 16), (16, 128), (64, 128), (17, 33), (32, 32), (32, 64), (64, 32), (64, 64),
                                         (48, 80), (128, 128), (96, 128), (128, 64), (256, 128), (128, 256), (192, 64),
                                         (160, 96), (224, 32), (16, 256), (256, 256)])
 def test_channel_classes_submanifold(mode, c_in, c_out):
