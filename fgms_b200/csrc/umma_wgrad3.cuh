@@ -431,13 +431,18 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   // keeps the diagonal.  Rows of at most 32 / 64 bytes: 4 pairs in slots of 32 / 64 bytes (a 64 x 64 accumulator,
   // or 128 x 128 for the 64-byte slots of fp16: one MMA per 64 pairs).  Longer rows whose
   // lengths are powers of two: 2 pairs, each row its own slot, while both fit one 128-row, 256-column accumulator
-  // (twice, so that two accumulators alternate).
+  // (twice, so that two accumulators alternate) and three packed stages of 128 pairs fit shared memory — else the
+  // shape is planned unpacked (second pass of the loop).
   const int a_row = c_in * es, b_row = c_out * es, max_row = a_row > b_row ? a_row : b_row;
   const bool pow2 = (a_row & (a_row - 1)) == 0 && (b_row & (b_row - 1)) == 0;
+  for (int attempt = 0; attempt < 2; ++attempt) {
   cfg->pack = 1; cfg->slot_a = cfg->slot_b = 0;
-  if (max_row <= 32) { cfg->pack = 4; cfg->slot_a = cfg->slot_b = 32; }
-  else if (max_row <= 64) { cfg->pack = 4; cfg->slot_a = cfg->slot_b = 64; }
-  else if (pow2 && 2 * c_in <= 128 && 2 * c_out <= 256) { cfg->pack = 2; cfg->slot_a = a_row; cfg->slot_b = b_row; }
+  if (attempt == 0) {
+    if (max_row <= 32) { cfg->pack = 4; cfg->slot_a = cfg->slot_b = 32; }
+    else if (max_row <= 64) { cfg->pack = 4; cfg->slot_a = cfg->slot_b = 64; }
+    else if (pow2 && 2 * c_in <= 128 && 2 * c_out <= 256) { cfg->pack = 2; cfg->slot_a = a_row; cfg->slot_b = b_row; }
+    else continue;
+  }
   // rows and columns of the accumulator
   const int m_eff = cfg->pack > 1 ? cfg->pack * cfg->slot_a / es : c_in;
   const int n_eff = cfg->pack > 1 ? cfg->pack * cfg->slot_b / es : c_out;
@@ -449,7 +454,7 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   cfg->n_acc = (n_eff + epr - 1) / epr * epr;
   cfg->pbp = cfg->n_acc / epr;
   const int buf_cols = cfg->n_mtile * cfg->n_acc;
-  if (buf_cols > 512) return false;
+  if (buf_cols > 512) { if (cfg->pack > 1) continue; return false; }
   cfg->n_buf = 4 * buf_cols <= 512 ? 4 : (2 * buf_cols <= 512 ? 2 : 1);
   cfg->buf_shift = cfg->n_buf == 4 ? 2 : (cfg->n_buf == 2 ? 1 : 0);
   // pairs per stage: 4, 8, 16 or 32 rows per producer warp (packed stages: always 32, the stage is small)
@@ -460,6 +465,7 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   while (pb > (cfg->pack > 1 ? 128 : 32) && (max_smem - fixed) / (pb * row_bytes) < 3) pb >>= 1;
   int n_stage = (max_smem - fixed) / (pb * row_bytes);
   if (n_stage > W3_MAX_STAGES) n_stage = W3_MAX_STAGES;
+  if (cfg->pack > 1 && n_stage < 3) continue;  // too large packed: plan it unpacked
   if (n_stage < 2) return false;
   // stages per commit: as many as leave three groups in flight
   cfg->group = 1;
@@ -469,6 +475,8 @@ inline bool w3_plan(int c_in, int c_out, int es, int k_vol, int max_smem, W3Conf
   cfg->n_stage = n_stage;
   cfg->smem = fixed + n_stage * pb * row_bytes;
   return true;
+  }
+  return false;
 }
 
 template <bool TF32, bool FULL, bool PACKED>
